@@ -52,13 +52,14 @@ __device__ __forceinline__ float silu_times(float g, float u) {
 
 // Activations that an epilogue may apply to its fp32 sums (after the bias): the precise library
 // functions, the same in every kernel that takes an activation code.
-enum { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_RELU = 4 };
+enum { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_RELU = 4, ACT_RELU_SQUARED = 5 };
 __device__ __forceinline__ float activate(float z, int act) {
   switch (act) {
     case ACT_GELU_ERF: return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));  // the exact gelu: z Phi(z)
     case ACT_GELU_TANH: return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
     case ACT_SILU: return z / (1.0f + expf(-z));
     case ACT_RELU: return fmaxf(z, 0.f);
+    case ACT_RELU_SQUARED: { const float r = fmaxf(z, 0.f); return r * r; }
     default: return z;
   }
 }

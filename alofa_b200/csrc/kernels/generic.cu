@@ -284,7 +284,7 @@ template <typename T>
 __global__ void __launch_bounds__(128) paged_attention_generic_kernel(
     T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
-    int max_blocks, int page_size, int nh, int nkv, int hd, int vd, int window, float scale, float softcap) {
+    int max_blocks, int page_size, int nh, int nkv, int hd, int vd, int window, float scale, float softcap, const float* __restrict__ sink) {
   extern __shared__ float smem[];
   float* qs = smem;          // hd
   float* ps = smem + hd;     // 128
@@ -297,7 +297,8 @@ __global__ void __launch_bounds__(128) paged_attention_generic_kernel(
   for (int d = tid; d < hd; d += 128) qs[d] = to_f(q[((size_t)t * nh + h) * hd + d]);
   int first = 0;
   if (window > 0 && P - window + 1 > 0) first = P - window + 1;
-  float m = -INFINITY, l = 0.f;
+  // a sink is one more term of the softmax's denominator, exp(sink[h]), that belongs to no key and has no value
+  float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
   float acc0 = 0.f, acc1 = 0.f;  // dims tid and tid + 128
   __syncthreads();
   for (int c0 = (first / 128) * 128; c0 <= P; c0 += 128) {
@@ -344,7 +345,7 @@ __global__ void __launch_bounds__(128) paged_attention_generic_kernel(
 ALOFA_API int alofa_paged_attention_generic(void* out, const void* q, const void* k_cache, const void* v_cache,
                                             const int* positions, const int* seq_of_token, const int* block_table,
                                             int max_blocks, int page_size, int n_tokens, int nh, int nkv, int hd,
-                                            int vd, int window, float scale, float softcap, int is_bf16, cudaStream_t stream) {
+                                            int vd, int window, float scale, float softcap, const float* sink, int is_bf16, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
   if (hd <= 0 || vd <= 0 || vd > 256 || nkv <= 0 || nh % nkv != 0 || page_size <= 0) return ALOFA_ERR_ARGUMENT;
   dim3 grid(n_tokens, nh);
@@ -352,10 +353,10 @@ ALOFA_API int alofa_paged_attention_generic(void* out, const void* q, const void
   if (is_bf16)
     paged_attention_generic_kernel<bf16><<<grid, 128, smem, stream>>>(
         (bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, positions, seq_of_token, block_table,
-        max_blocks, page_size, nh, nkv, hd, vd, window, scale, softcap);
+        max_blocks, page_size, nh, nkv, hd, vd, window, scale, softcap, sink);
   else
     paged_attention_generic_kernel<float><<<grid, 128, smem, stream>>>(
         (float*)out, (const float*)q, (const float*)k_cache, (const float*)v_cache, positions, seq_of_token, block_table,
-        max_blocks, page_size, nh, nkv, hd, vd, window, scale, softcap);
+        max_blocks, page_size, nh, nkv, hd, vd, window, scale, softcap, sink);
   return launch_status();
 }

@@ -23,11 +23,18 @@
 // position p turns by the angle p * f_i, f_i given as fp32.  Angle, cosine and
 // sine are fp32 (the precise library functions).
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void turn(float u, float v, float angle, float& a, float& b) {
+__device__ __forceinline__ void turn(float u, float v, float angle, float& a, float& b, float mag = 1.0f) {
   float s, c;
   sincosf(angle, &s, &c);
+  s *= mag;  // a factor on cosine and sine alike (1: none), as scaled rotary encodings have
+  c *= mag;
   a = u * c - v * s;
   b = v * c + u * s;
+}
+// Which two numbers pair i of a rotated part of `dims` numbers joins: neighbours (2i, 2i + 1), or (halves) i and i + dims / 2.
+__device__ __forceinline__ void pair_of(int i, int dims, int halves, int& lo, int& hi) {
+  lo = halves ? i : 2 * i;
+  hi = halves ? i + dims / 2 : 2 * i + 1;
 }
 
 // ---------------------------------------------------------------------------
@@ -42,16 +49,18 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(T* __restrict__ cq,
                                                              const float* __restrict__ wq, const float* __restrict__ wkv,
                                                              const float* __restrict__ freq, const int* __restrict__ positions,
                                                              const int* __restrict__ slot_map, int q_rank, int kv_rank, int rot, int rot_dims,
-                                                             float eps) {
+                                                             float eps, int ld, int halves, float mag) {
   __shared__ float scratch[32];
   pdl_begin();
   const int t = blockIdx.x;
-  const float* row = lat + (size_t)t * (q_rank + kv_rank + rot);
+  const float* row = lat + (size_t)t * ld;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < q_rank; c += blockDim.x) ss = fmaf(row[c], row[c], ss);
-  ss = block_sum(ss, scratch);
-  const float fq = 1.0f / sqrtf(ss / (float)q_rank + eps);
-  for (int c = threadIdx.x; c < q_rank; c += blockDim.x) cq[(size_t)t * q_rank + c] = from_f<T>(row[c] * fq * wq[c]);
+  if (q_rank > 0) {  // a design without a query latent has q_rank 0
+    for (int c = threadIdx.x; c < q_rank; c += blockDim.x) ss = fmaf(row[c], row[c], ss);
+    ss = block_sum(ss, scratch);
+    const float fq = 1.0f / sqrtf(ss / (float)q_rank + eps);
+    for (int c = threadIdx.x; c < q_rank; c += blockDim.x) cq[(size_t)t * q_rank + c] = from_f<T>(row[c] * fq * wq[c]);
+  }
   if (!cache) return;
   const int slot = slot_map[t];
   if (slot < 0) return;
@@ -66,24 +75,26 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(T* __restrict__ cq,
   const float* kr = kv + kv_rank;
   for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) {
     float a, b;
-    turn(kr[2 * i], kr[2 * i + 1], p * freq[i], a, b);
-    out[kv_rank + 2 * i] = from_f<T>(a);
-    out[kv_rank + 2 * i + 1] = from_f<T>(b);
+    int lo, hi;
+    pair_of(i, rot_dims, halves, lo, hi);
+    turn(kr[lo], kr[hi], p * freq[i], a, b, mag);
+    out[kv_rank + lo] = from_f<T>(a);
+    out[kv_rank + hi] = from_f<T>(b);
   }
   for (int c = rot_dims + threadIdx.x; c < rot; c += blockDim.x) out[kv_rank + c] = from_f<T>(kr[c]);
 }
 
 ALOFA_API int alofa_latent_prepare(void* cq, void* cache, const float* lat, const float* wq, const float* wkv, const float* freq,
                                    const int* positions, const int* slot_map, int n_tokens, int q_rank, int kv_rank, int rot, int rot_dims,
-                                   float eps, int is_bf16, cudaStream_t stream) {
+                                   float eps, int ld, int halves, float mag, int is_bf16, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
-  if (q_rank <= 0 || kv_rank <= 0 || rot < 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1)) return ALOFA_ERR_ARGUMENT;
+  if (q_rank < 0 || kv_rank <= 0 || rot < 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1) || ld < q_rank + kv_rank + rot) return ALOFA_ERR_ARGUMENT;
   if (is_bf16)
     launch_dep(latent_prepare_kernel<bf16>, n_tokens, 256, 0, stream, (bf16*)cq, (bf16*)cache, lat, wq, wkv, freq, positions, slot_map, q_rank, kv_rank,
-               rot, rot_dims, eps);
+               rot, rot_dims, eps, ld, halves, mag);
   else
     launch_dep(latent_prepare_kernel<float>, n_tokens, 256, 0, stream, (float*)cq, (float*)cache, lat, wq, wkv, freq, positions, slot_map, q_rank,
-               kv_rank, rot, rot_dims, eps);
+               kv_rank, rot, rot_dims, eps, ld, halves, mag);
   return launch_status();
 }
 
@@ -94,7 +105,8 @@ ALOFA_API int alofa_latent_prepare(void* cq, void* cache, const float* lat, cons
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void latent_query_turn_kernel(T* __restrict__ qa, const T* __restrict__ q, const float* __restrict__ freq,
-                                         const int* __restrict__ positions, int heads, int dim, int rot, int rot_dims, int kv_rank) {
+                                         const int* __restrict__ positions, int heads, int dim, int rot, int rot_dims, int kv_rank, int halves,
+                                         float mag) {
   pdl_begin();
   const int t = blockIdx.x;
   const float p = (float)positions[t];
@@ -104,9 +116,11 @@ __global__ void latent_query_turn_kernel(T* __restrict__ qa, const T* __restrict
     const T* src = q + ((size_t)t * heads + h) * (dim + rot) + dim;
     T* dst = qa + ((size_t)t * heads + h) * (kv_rank + rot) + kv_rank;
     float a, b;
-    turn(to_f(src[2 * i]), to_f(src[2 * i + 1]), p * freq[i], a, b);
-    dst[2 * i] = from_f<T>(a);
-    dst[2 * i + 1] = from_f<T>(b);
+    int lo, hi;
+    pair_of(i, rot_dims, halves, lo, hi);
+    turn(to_f(src[lo]), to_f(src[hi]), p * freq[i], a, b, mag);
+    dst[lo] = from_f<T>(a);
+    dst[hi] = from_f<T>(b);
   }
   const int rest = rot - rot_dims;
   for (int e = threadIdx.x; e < heads * rest; e += blockDim.x) {
@@ -116,13 +130,13 @@ __global__ void latent_query_turn_kernel(T* __restrict__ qa, const T* __restrict
 }
 
 ALOFA_API int alofa_latent_query_turn(void* qa, const void* q, const float* freq, const int* positions, int n_tokens, int heads, int dim, int rot,
-                                      int rot_dims, int kv_rank, int is_bf16, cudaStream_t stream) {
+                                      int rot_dims, int kv_rank, int halves, float mag, int is_bf16, cudaStream_t stream) {
   if (n_tokens <= 0 || rot <= 0) return ALOFA_OK;
   if (rot_dims < 0 || rot_dims > rot || (rot_dims & 1)) return ALOFA_ERR_ARGUMENT;
   if (is_bf16)
-    launch_dep(latent_query_turn_kernel<bf16>, n_tokens, 128, 0, stream, (bf16*)qa, (const bf16*)q, freq, positions, heads, dim, rot, rot_dims, kv_rank);
+    launch_dep(latent_query_turn_kernel<bf16>, n_tokens, 128, 0, stream, (bf16*)qa, (const bf16*)q, freq, positions, heads, dim, rot, rot_dims, kv_rank, halves, mag);
   else
-    launch_dep(latent_query_turn_kernel<float>, n_tokens, 128, 0, stream, (float*)qa, (const float*)q, freq, positions, heads, dim, rot, rot_dims, kv_rank);
+    launch_dep(latent_query_turn_kernel<float>, n_tokens, 128, 0, stream, (float*)qa, (const float*)q, freq, positions, heads, dim, rot, rot_dims, kv_rank, halves, mag);
   return launch_status();
 }
 

@@ -389,6 +389,9 @@ ALOFA_API int alofa_linear_scan(float* y, const float* v, int ldv, int v_off, co
 // multiplies either before the norm (gate_first: the gated values are what is normed) or after it.
 // One block per (token, part): as many threads as the part has groups of four numbers, up to 256.
 // ---------------------------------------------------------------------------
+// gate_first: bit 0 = the gate multiplies before the norm; bit 1 = the gate is sigmoid(g), not silu(g)
+__device__ __forceinline__ float gate_of(float z, int sigmoid) { return sigmoid ? 1.0f / (1.0f + expf(-z)) : silu_f(z); }
+
 template <typename TO>
 __global__ void __launch_bounds__(256) gated_group_norm_kernel(TO* __restrict__ out, const float* __restrict__ y, const float* __restrict__ gate, int ldg,
                                                                int g_off, const float* __restrict__ w, int wlen, int width, int groups, float eps,
@@ -402,14 +405,14 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(TO* __restrict__ 
   float ss = 0.f;
   for (int c = lo + threadIdx.x; c < lo + part; c += blockDim.x) {
     float v = yr[c];
-    if (gr && gate_first) v *= silu_f(gr[c]);
+    if (gr && (gate_first & 1)) v *= gate_of(gr[c], gate_first & 2);
     ss = fmaf(v, v, ss);
   }
   ss = block_sum(ss, scratch);
   const float r = 1.0f / sqrtf(ss / (float)part + eps);
   for (int c = lo + threadIdx.x; c < lo + part; c += blockDim.x) {
     float v = yr[c];
-    if (gr) v *= silu_f(gr[c]);  // before or after the norm, the gate is a factor of the result
+    if (gr) v *= gate_of(gr[c], gate_first & 2);  // before or after the norm, the gate is a factor of the result
     out[(size_t)t * width + c] = from_f<TO>(v * r * w[c % wlen]);
   }
 }
@@ -476,7 +479,8 @@ ALOFA_API int alofa_branch_norm_add(float* h, const float* ya, const float* wa, 
 template <typename T>
 __global__ void __launch_bounds__(256) qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const float* __restrict__ qkv,
                                                           const int* __restrict__ positions, const int* __restrict__ slot_map, int H, int G, int d, int dv,
-                                                          int qk_norm, float eps, float coef, int every, int n_tokens) {
+                                                          int qk_norm, float eps, float coef, int every, int n_tokens,
+                                                          const float* __restrict__ freq, int rot_dims) {
   pdl_begin();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int per = H + 2 * G;
@@ -501,7 +505,18 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(T* __restrict__ q_out,
     } else {
       to = k_cache + ((size_t)slot_map[t] * G + (u - H)) * d;
     }
-    for (int c = lane; c < d; c += 32) to[c] = from_f<T>(x[c] * mul);
+    if (rot_dims > 0) {
+      // neighbouring pairs (2i, 2i + 1), i < rot_dims / 2, turned by the angle p * freq[i] (an fp32 product, precise sine and cosine)
+      const float p = (float)positions[t];
+      for (int i = lane; i < rot_dims / 2; i += 32) {
+        float sn, cs;
+        sincosf(p * freq[i], &sn, &cs);
+        const float a = x[2 * i] * mul, b = x[2 * i + 1] * mul;
+        to[2 * i] = from_f<T>(a * cs - b * sn);
+        to[2 * i + 1] = from_f<T>(b * cs + a * sn);
+      }
+    }
+    for (int c = rot_dims + lane; c < d; c += 32) to[c] = from_f<T>(x[c] * mul);
   } else {
     const int gi = u - H - G;
     const float* x = row + (size_t)(H + G) * d + (size_t)gi * dv;
@@ -511,16 +526,18 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(T* __restrict__ q_out,
 }
 
 ALOFA_API int alofa_qkv_prepare(void* q_out, void* k_cache, void* v_cache, const float* qkv, const int* positions, const int* slot_map, int n_tokens, int H, int G,
-                                int d, int dv, int qk_norm, float eps, float coef, int every, int is_bf16, cudaStream_t stream) {
+                                int d, int dv, int qk_norm, float eps, float coef, int every, const float* freq, int rot_dims, int is_bf16,
+                                cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
-  if (H <= 0 || G <= 0 || d <= 0 || dv <= 0 || (coef != 0.f && every <= 0)) return ALOFA_ERR_ARGUMENT;
+  if (H <= 0 || G <= 0 || d <= 0 || dv <= 0 || (coef != 0.f && every <= 0) || rot_dims < 0 || rot_dims > d || (rot_dims & 1) || (rot_dims && !freq))
+    return ALOFA_ERR_ARGUMENT;
   const long long units = (long long)n_tokens * (H + 2 * G);
   const unsigned blocks = (unsigned)((units + 7) / 8);
   if (is_bf16)
     launch_dep(qkv_prepare_kernel<bf16>, blocks, 256, 0, stream, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, qkv, positions, slot_map, H, G, d, dv, qk_norm, eps, coef,
-               every, n_tokens);
+               every, n_tokens, freq, rot_dims);
   else
     launch_dep(qkv_prepare_kernel<float>, blocks, 256, 0, stream, (float*)q_out, (float*)k_cache, (float*)v_cache, qkv, positions, slot_map, H, G, d, dv, qk_norm, eps,
-               coef, every, n_tokens);
+               coef, every, n_tokens, freq, rot_dims);
   return launch_status();
 }

@@ -41,7 +41,7 @@ def _generic():
             "alofa_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _P],
             "alofa_gemm_generic": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
             "alofa_rope_store": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-            "alofa_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
+            "alofa_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P, _I, _P],
         }
         for name, args in sigs.items():
             fn = getattr(lib, name)
@@ -265,11 +265,13 @@ def rope_store(q_out, k_cache, v_cache, qkv, cos_sin, positions, slot_map, nh, n
     )
 
 
-def paged_attention_generic(out, q, k_cache, v_cache, positions, seq_of_token, block_table, page_size, nh, nkv, hd, window, scale, softcap: float = 0.0, vd=None) -> None:
+def paged_attention_generic(out, q, k_cache, v_cache, positions, seq_of_token, block_table, page_size, nh, nkv, hd, window, scale, softcap: float = 0.0, vd=None, sink=None) -> None:
     """Causal grouped-query attention over the paged cache for every size and
     both dtypes; fp32 scores and softmax.  ``softcap`` > 0 bounds the scaled
     scores by ``softcap * tanh(score / softcap)``; ``vd`` is the values' head
-    size when it differs from the keys' ``hd``."""
+    size when it differs from the keys' ``hd``; ``sink`` (fp32, one score per
+    head) adds ``exp(sink[h])`` to the softmax's denominator, a term that
+    belongs to no key and has no value."""
     n = q.shape[0]
     vd = hd if vd is None else vd
     dt = q.dtype
@@ -279,7 +281,8 @@ def paged_attention_generic(out, q, k_cache, v_cache, positions, seq_of_token, b
         _generic().alofa_paged_attention_generic(
             _dev(out, "out", dt), _dev(q, "q"), _dev(k_cache, "k_cache", dt), _dev(v_cache, "v_cache", dt),
             _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32), _dev(block_table, "block_table", torch.int32),
-            block_table.shape[1], page_size, n, nh, nkv, hd, vd, int(window or 0), float(scale), float(softcap or 0.0), _is_bf16(q, "q"), _stream(),
+            block_table.shape[1], page_size, n, nh, nkv, hd, vd, int(window or 0), float(scale), float(softcap or 0.0),
+            _dev(sink, "sink", torch.float32) if sink is not None else None, _is_bf16(q, "q"), _stream(),
         ),
         "paged_attention_generic", f"heads={nh} kv_heads={nkv} head_dim={hd} v_head_dim={vd}",
     )
@@ -553,7 +556,7 @@ def splitk_reduce(out, partial, bias, splits: int, epi: int) -> None:
 
 
 # -- latent attention, sandwich norms, routed feed-forwards -------------------------------------------
-ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "silu": 3, "relu": 4}
+ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "silu": 3, "relu": 4, "relu_squared": 5}
 _L = ctypes.c_longlong
 
 
@@ -562,8 +565,8 @@ def _latent():
     if lib is None:
         lib = load_library("alofa_latent", ["kernels/latent.cu", "kernels/gemm_batched_bf16.cu"])
         sigs = {
-            "alofa_latent_prepare": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
-            "alofa_latent_query_turn": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+            "alofa_latent_prepare": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _F, _I, _P],
+            "alofa_latent_query_turn": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
             "alofa_rotary_interleaved": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
             "alofa_gemm_batched": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _I, _I, _I, _I, _I, _P],
             "alofa_gemm_batched_bf16": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _I, _I, _I, _P],
@@ -586,28 +589,38 @@ def _latent():
     return lib
 
 
-def latent_prepare(cq, cache_rows, lat, wq, wkv, freq, positions, slot_map, q_rank: int, kv_rank: int, rot: int, rot_dims: int, eps: float) -> None:
-    """From the stacked down-projection ``lat`` [T, q_rank + kv_rank + rot]
-    (fp32): ``cq`` = RMSNorm of the first part; the cache row of each token =
-    [RMSNorm of the second part | the third part, its first ``rot_dims``
-    numbers turned by the token's position].  ``cache_rows`` None: no write."""
+def latent_prepare(cq, cache_rows, lat, wq, wkv, freq, positions, slot_map, q_rank: int, kv_rank: int, rot: int, rot_dims: int, eps: float,
+                   halves: bool = False, mag: float = 1.0) -> None:
+    """From the stacked down-projection ``lat`` [T, >= q_rank + kv_rank + rot]
+    (fp32; further columns are not read): ``cq`` = RMSNorm of the first part
+    (``q_rank`` 0: there is none, ``cq`` and ``wq`` are None); the cache row of
+    each token = [RMSNorm of the second part | the third part, its first
+    ``rot_dims`` numbers turned by the token's position: neighbouring pairs, or
+    with ``halves`` number i with number i + rot_dims / 2; cosine and sine
+    times ``mag``].  ``cache_rows`` None: no write."""
     f32 = torch.float32
     n = lat.shape[0]
-    if lat.shape[1] != q_rank + kv_rank + rot or tuple(cq.shape) != (n, q_rank) or (cache_rows is not None and cache_rows.shape[1] != kv_rank + rot):
-        raise AlofaError("invalid_argument", "latent_prepare sizes disagree", f"lat={tuple(lat.shape)} cq={tuple(cq.shape)}")
+    if lat.shape[1] < q_rank + kv_rank + rot or (q_rank and tuple(cq.shape) != (n, q_rank)) or (cache_rows is not None and cache_rows.shape[1] != kv_rank + rot):
+        raise AlofaError("invalid_argument", "latent_prepare sizes disagree", f"lat={tuple(lat.shape)} q_rank={q_rank} kv_rank={kv_rank} rot={rot}")
+    if q_rank == 0 and cache_rows is None:
+        return
+    dt = cq.dtype if q_rank else cache_rows.dtype
     _done(
         _latent().alofa_latent_prepare(
-            _dev(cq, "cq"), _dev(cache_rows, "cache", cq.dtype) if cache_rows is not None else None, _dev(lat, "lat", f32), _dev(wq, "wq", f32),
+            _dev(cq, "cq") if q_rank else None, _dev(cache_rows, "cache", dt) if cache_rows is not None else None, _dev(lat, "lat", f32),
+            _dev(wq, "wq", f32) if q_rank else None,
             _dev(wkv, "wkv", f32), _dev(freq, "freq", f32) if rot_dims else None, _dev(positions, "positions", torch.int32),
-            _dev(slot_map, "slot_map", torch.int32) if cache_rows is not None else None, n, q_rank, kv_rank, rot, rot_dims, float(eps), _is_bf16(cq, "cq"), _stream(),
+            _dev(slot_map, "slot_map", torch.int32) if cache_rows is not None else None, n, q_rank, kv_rank, rot, rot_dims, float(eps), lat.shape[1],
+            1 if halves else 0, float(mag), 1 if dt == torch.bfloat16 else 0, _stream(),
         ),
         "latent_prepare",
     )
 
 
-def latent_query_turn(qa, q, freq, positions, heads: int, dim: int, rot: int, rot_dims: int, kv_rank: int) -> None:
+def latent_query_turn(qa, q, freq, positions, heads: int, dim: int, rot: int, rot_dims: int, kv_rank: int, halves: bool = False, mag: float = 1.0) -> None:
     """The rotated part of q [T, heads * (dim + rot)] turned by position into
-    columns ``kv_rank``.. of qa [T, heads * (kv_rank + rot)]."""
+    columns ``kv_rank``.. of qa [T, heads * (kv_rank + rot)]; ``halves`` and
+    ``mag`` as in :func:`latent_prepare`."""
     n = q.shape[0]
     if q.shape[1] != heads * (dim + rot) or tuple(qa.shape) != (n, heads * (kv_rank + rot)):
         raise AlofaError("invalid_argument", "latent_query_turn sizes disagree", f"q={tuple(q.shape)} qa={tuple(qa.shape)}")
@@ -615,7 +628,8 @@ def latent_query_turn(qa, q, freq, positions, heads: int, dim: int, rot: int, ro
         return
     _done(
         _latent().alofa_latent_query_turn(_dev(qa, "qa", q.dtype), _dev(q, "q"), _dev(freq, "freq", torch.float32) if rot_dims else None,
-                                          _dev(positions, "positions", torch.int32), n, heads, dim, rot, rot_dims, kv_rank, _is_bf16(q, "q"), _stream()),
+                                          _dev(positions, "positions", torch.int32), n, heads, dim, rot, rot_dims, kv_rank, 1 if halves else 0, float(mag),
+                                          _is_bf16(q, "q"), _stream()),
         "latent_query_turn",
     )
 
@@ -880,7 +894,7 @@ def _recurrent():
             "alofa_linear_scan": [_P, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _F, _F, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
             "alofa_gated_group_norm": [_P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P],
             "alofa_branch_norm_add": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _P],
-            "alofa_qkv_prepare": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
+            "alofa_qkv_prepare": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _I, _I, _P],
         }
         for name, args in sigs.items():
             fn = getattr(lib, name)
@@ -982,11 +996,12 @@ def linear_scan_work(rows: int, heads: int, n: int, mode: int) -> int:
     return rows * (heads * n if mode else 2 * heads)
 
 
-def gated_group_norm(out, y, gate, g_off: int, w, groups: int, eps: float, gate_first: bool) -> None:
+def gated_group_norm(out, y, gate, g_off: int, w, groups: int, eps: float, gate_first: bool, sigmoid: bool = False) -> None:
     """out = rows of y [T, width] normed in ``groups`` equal parts (each by
     its own root mean square), times ``w[c % len(w)]``, with the gate
     ``silu(gate[t, g_off + c])`` multiplied in before the norm
-    (``gate_first``) or after it; fp32 in, out in its own dtype."""
+    (``gate_first``) or after it (``sigmoid``: the gate is ``sigmoid(.)``
+    instead); fp32 in, out in its own dtype."""
     n, width = y.shape
     f32 = torch.float32
     if tuple(out.shape) != (n, width) or (gate is not None and (gate.shape[0] != n or g_off + width > gate.shape[1])):
@@ -994,7 +1009,7 @@ def gated_group_norm(out, y, gate, g_off: int, w, groups: int, eps: float, gate_
     _done(
         _recurrent().alofa_gated_group_norm(_dev(out, "out"), _dev(y, "y", f32), _dev(gate, "gate", f32) if gate is not None else None,
                                             gate.shape[1] if gate is not None else 0, g_off, _dev(w, "w", f32), w.shape[0], n, width, groups, float(eps),
-                                            1 if gate_first else 0, _is_bf16(out, "out"), _stream()),
+                                            (1 if gate_first else 0) | (2 if sigmoid else 0), _is_bf16(out, "out"), _stream()),
         "gated_group_norm", f"width={width} groups={groups}",
     )
 
@@ -1012,11 +1027,14 @@ def branch_norm_add(h, ya, wa, yb, wb, eps: float, scale: float) -> None:
     )
 
 
-def qkv_prepare(q_out, k_cache, v_cache, qkv, positions, slot_map, heads: int, kv_heads: int, d: int, dv: int, qk_norm: bool, eps: float, coef: float, every: int) -> None:
+def qkv_prepare(q_out, k_cache, v_cache, qkv, positions, slot_map, heads: int, kv_heads: int, d: int, dv: int, qk_norm: bool, eps: float, coef: float, every: int,
+                freq=None, rot_dims: int = 0) -> None:
     """From the fp32 sums of a stacked projection [q | k | v]: q and k divided
     by their root mean square per head (``qk_norm``), q times ``1 + coef *
-    ln(floor((p + 1) / every) + 1)`` at position p, q to ``q_out``, k and v to
-    the tokens' cache slots; out tensors in the compute dtype."""
+    ln(floor((p + 1) / every) + 1)`` at position p, the first ``rot_dims``
+    numbers of every q and k head turned by the position (neighbouring pairs,
+    pair i by the angle ``p * freq[i]``), q to ``q_out``, k and v to the
+    tokens' cache slots; out tensors in the compute dtype."""
     n = qkv.shape[0]
     dt = q_out.dtype
     if qkv.shape[1] != heads * d + kv_heads * (d + dv) or tuple(q_out.shape) != (n, heads * d) or tuple(k_cache.shape[1:]) != (kv_heads, d) or tuple(v_cache.shape[1:]) != (kv_heads, dv):
@@ -1024,6 +1042,158 @@ def qkv_prepare(q_out, k_cache, v_cache, qkv, positions, slot_map, heads: int, k
     _done(
         _recurrent().alofa_qkv_prepare(_dev(q_out, "q_out"), _dev(k_cache, "k_cache", dt), _dev(v_cache, "v_cache", dt), _dev(qkv, "qkv", torch.float32),
                                        _dev(positions, "positions", torch.int32), _dev(slot_map, "slot_map", torch.int32), n, heads, kv_heads, d, dv,
-                                       1 if qk_norm else 0, float(eps), float(coef), int(every), _is_bf16(q_out, "q_out"), _stream()),
+                                       1 if qk_norm else 0, float(eps), float(coef), int(every),
+                                       _dev(freq, "freq", torch.float32) if rot_dims else None, int(rot_dims), _is_bf16(q_out, "q_out"), _stream()),
         "qkv_prepare",
     )
+
+
+def _hyper():
+    lib = _libs.get("hyper")
+    if lib is None:
+        lib = load_library("alofa_hyper", ["kernels/hyper.cu"])
+        sigs = {
+            "alofa_hyper_connect": [_P, _L, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _I, _P],
+            "alofa_streams_fill": [_P, _L, _P, _L, _I, _P],
+            "alofa_scaled_sum": [_P, _P, _F, _P, _F, _L, _I, _P],
+            "alofa_scale_rows": [_P, _F, _L, _P],
+            "alofa_head_gate": [_P, _P, _I, _I, _I, _I, _I, _I, _P],
+        }
+        for name, args in sigs.items():
+            fn = getattr(lib, name)
+            fn.restype = _I
+            fn.argtypes = args
+        _libs["hyper"] = lib
+    return lib
+
+
+HYPER_MAX_STREAMS = 8
+
+
+def hyper_connect(streams, y=None, mix=None, out_w=None, in_w=None, norm_w=None, eps: float = 0.0, x_out=None, sum_out=None) -> None:
+    """One pass over several residual streams ``streams`` [S, T, W] (fp32), any
+    subset of: with ``y`` [T, W] (a sublayer's output) every stream moves at
+    once, ``x_t <- sum_s mix[s, t] x_s + out_w[t] y``; with ``x_out`` the next
+    sublayer's input ``rmsnorm(sum_s in_w[s] x_s) * norm_w`` is written in
+    ``x_out``'s dtype; with ``sum_out`` (fp32 [T, W]) the streams' sum."""
+    f32 = torch.float32
+    S, n, width = streams.shape
+    if streams.dtype != f32 or not streams.is_cuda or streams.stride(2) != 1 or streams.stride(1) != width:
+        raise AlofaError("invalid_argument", "hyper_connect wants fp32 streams [S, T, W] with packed rows")
+    for t_, name in ((y, "y"), (x_out, "x_out"), (sum_out, "sum_out")):
+        if t_ is not None and tuple(t_.shape) != (n, width):
+            raise AlofaError("invalid_argument", "hyper_connect sizes disagree", f"{name}={tuple(t_.shape)} streams={tuple(streams.shape)}")
+    if (y is not None and (tuple(mix.shape) != (S, S) or out_w.shape[0] != S)) or (x_out is not None and (in_w.shape[0] != S or norm_w.shape[0] != width)):
+        raise AlofaError("invalid_argument", "hyper_connect weights disagree with the streams", f"S={S} width={width}")
+    _done(
+        _hyper().alofa_hyper_connect(
+            streams.data_ptr(), streams.stride(0), _dev(y, "y", f32) if y is not None else None, _dev(mix, "mix", f32) if y is not None else None,
+            _dev(out_w, "out_w", f32) if y is not None else None, _dev(in_w, "in_w", f32) if x_out is not None else None,
+            _dev(norm_w, "norm_w", f32) if x_out is not None else None, float(eps), _dev(x_out, "x_out") if x_out is not None else None,
+            _dev(sum_out, "sum_out", f32) if sum_out is not None else None, n, S, width, _is_bf16(x_out, "x_out") if x_out is not None else 0, _stream(),
+        ),
+        "hyper_connect", f"S={S} width={width}",
+    )
+
+
+def streams_fill(streams, h) -> None:
+    """streams[s] = h for every s: streams [S, T, W] fp32, h [T, W] fp32."""
+    if tuple(streams.shape[1:]) != tuple(h.shape) or streams.dtype != torch.float32 or streams.stride(1) != h.shape[1] or streams.stride(2) != 1:
+        raise AlofaError("invalid_argument", "streams_fill sizes disagree", f"streams={tuple(streams.shape)} h={tuple(h.shape)}")
+    _done(_hyper().alofa_streams_fill(streams.data_ptr(), streams.stride(0), _dev(h, "h", torch.float32), h.numel(), streams.shape[0], _stream()), "streams_fill")
+
+
+def scaled_sum(out, ya, sa: float, yb=None, sb: float = 0.0, accumulate: bool = False) -> None:
+    """out (+)= sa * ya + sb * yb, fp32, same shapes (``yb`` may be None)."""
+    f32 = torch.float32
+    if out.shape != ya.shape or (yb is not None and yb.shape != ya.shape):
+        raise AlofaError("invalid_argument", "scaled_sum sizes disagree", f"out={tuple(out.shape)} ya={tuple(ya.shape)}")
+    _done(_hyper().alofa_scaled_sum(_dev(out, "out", f32), _dev(ya, "ya", f32), float(sa), _dev(yb, "yb", f32) if yb is not None else None, float(sb), out.numel(),
+                                    1 if accumulate else 0, _stream()), "scaled_sum")
+
+
+def scale_rows(x, scale: float) -> None:
+    """x *= scale (fp32, in place)."""
+    _done(_hyper().alofa_scale_rows(_dev(x, "x", torch.float32), float(scale), x.numel(), _stream()), "scale_rows")
+
+
+def head_gate(o, gate, g_off: int, heads: int, vdim: int) -> None:
+    """o[t, h, :] *= sigmoid(gate[t, g_off + h]) in place: o [T, heads * vdim]
+    in its own dtype, gate fp32 [T, ld] (sums of a projection)."""
+    n = o.shape[0]
+    if o.shape[1] != heads * vdim or gate.shape[0] != n or g_off + heads > gate.shape[1]:
+        raise AlofaError("invalid_argument", "head_gate sizes disagree", f"o={tuple(o.shape)} gate={tuple(gate.shape)}")
+    _done(_hyper().alofa_head_gate(_dev(o, "o"), _dev(gate, "gate", torch.float32), gate.shape[1], g_off, n, heads, vdim, _is_bf16(o, "o"), _stream()), "head_gate")
+
+
+def _delta():
+    lib = _libs.get("delta")
+    if lib is None:
+        lib = load_library("alofa_delta", ["kernels/delta.cu"])
+        sigs = {
+            "alofa_min_gru": [_P, _P, _I, _I, _I, _I, _P, _L, _P, _P, _I, _I, _I, _P],
+            "alofa_delta_prepare": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _F, _P],
+            "alofa_delta_scan": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        }
+        for name, args in sigs.items():
+            fn = getattr(lib, name)
+            fn.restype = _I
+            fn.argtypes = args
+        _libs["delta"] = lib
+    return lib
+
+
+def _slot_state(state, words: int, what: str) -> None:
+    if state.dtype != torch.float32 or not state.is_cuda or state.stride(-1) != 1 or state.stride(0) < words:
+        raise AlofaError("invalid_argument", f"{what} needs an fp32 state on the device with room for every slot", f"state={tuple(state.shape)} words={words}")
+
+
+def min_gru(out, u, z_off: int, x_off: int, g_off: int, state, q_start, state_slots, n_seqs: int) -> None:
+    """Element by element over each request's tokens of the step in order:
+    ``z = sigmoid(u[t, z_off + c])``, ``x = u[t, x_off + c]``, the candidate
+    ``x + 1/2`` where ``x >= 0`` and ``sigmoid(x)`` below, ``S = (1 - z) S + z
+    * candidate``, ``out[t, c] = S * silu(u[t, g_off + c])``.  u fp32 [T, ld];
+    out [T, width] in its own dtype; state [slots, >= width] fp32, read and
+    left up to date."""
+    n, width = out.shape
+    i32 = torch.int32
+    if u.shape[0] != n or max(z_off, x_off, g_off) + width > u.shape[1]:
+        raise AlofaError("invalid_argument", "min_gru sizes disagree", f"out={tuple(out.shape)} u={tuple(u.shape)}")
+    _slot_state(state, width, "min_gru")
+    _done(_delta().alofa_min_gru(_dev(out, "out"), _dev(u, "u", torch.float32), u.shape[1], z_off, x_off, g_off, state.data_ptr(), state.stride(0),
+                                 _dev(q_start, "q_start", i32), _dev(state_slots, "state_slots", i32), n_seqs, width, _is_bf16(out, "out"), _stream()), "min_gru")
+
+
+def delta_prepare(qn, kn, kq, g, beta, conv, dz, u, b_off: int, dt_bias, a_log, heads: int, groups: int, n: int, unit_eps: float, q_scale: float) -> None:
+    """What :func:`delta_scan` reads, all fp32: from conv [T, ld] = [q: groups *
+    n | k: groups * n | v ...] the unit vectors ``qn = q / sqrt(sum q^2 +
+    unit_eps) * q_scale`` and ``kn`` (no scale) per group, ``kq = kn . qn``;
+    from the first heads * n columns of dz [T, ld''] the decays ``g = exp(-exp(a_log[h]) * softplus(dz +
+    dt_bias))``; from u [T, ld'] ``beta = sigmoid(u[t, b_off + h])``."""
+    f32 = torch.float32
+    rows = conv.shape[0]
+    if (tuple(qn.shape) != (rows, groups * n) or tuple(kn.shape) != (rows, groups * n) or tuple(kq.shape) != (rows, groups) or tuple(g.shape) != (rows, heads * n)
+            or tuple(beta.shape) != (rows, heads) or dz.shape[0] != rows or dz.shape[1] < heads * n or conv.shape[1] < 2 * groups * n or u.shape[0] != rows
+            or b_off + heads > u.shape[1] or dt_bias.shape[0] != heads * n or a_log.shape[0] != heads):
+        raise AlofaError("invalid_argument", "delta_prepare sizes disagree", f"conv={tuple(conv.shape)} dz={tuple(dz.shape)} heads={heads} groups={groups} n={n}")
+    _done(_delta().alofa_delta_prepare(_dev(qn, "qn", f32), _dev(kn, "kn", f32), _dev(kq, "kq", f32), _dev(g, "g", f32), _dev(beta, "beta", f32), _dev(conv, "conv", f32),
+                                       conv.shape[1], _dev(dz, "dz", f32), dz.shape[1], _dev(u, "u", f32), u.shape[1], b_off, _dev(dt_bias, "dt_bias", f32), _dev(a_log, "a_log", f32),
+                                       rows, heads, groups, n, float(unit_eps), float(q_scale), _stream()), "delta_prepare")
+
+
+def delta_scan(y, v, v_off: int, kn, qn, kq, g, beta, state, q_start, state_slots, n_seqs: int, heads: int, groups: int, n: int, p: int, spread: int = 0) -> None:
+    """The gated delta rule per head over each request's tokens of the step in
+    order, all fp32: ``S <- diag(g_t) S; u = beta_t (v_t - S^T k_t); S <- S +
+    k_t u^T; y_t = S^T q_t``.  The state [slots, >= heads * p * n] (per head
+    [p][n]) is read and left up to date; v fp32 [T, ld] at column offset
+    ``v_off`` (heads * p columns); head h reads the keys and queries of group
+    ``h // (heads / groups)``."""
+    f32, i32 = torch.float32, torch.int32
+    rows = y.shape[0]
+    if (tuple(y.shape) != (rows, heads * p) or v.shape[0] != rows or v_off + heads * p > v.shape[1] or tuple(kn.shape) != (rows, groups * n)
+            or tuple(qn.shape) != (rows, groups * n) or tuple(kq.shape) != (rows, groups) or tuple(g.shape) != (rows, heads * n) or tuple(beta.shape) != (rows, heads)):
+        raise AlofaError("invalid_argument", "delta_scan sizes disagree", f"y={tuple(y.shape)} v={tuple(v.shape)} heads={heads} groups={groups} n={n} p={p}")
+    _slot_state(state, heads * p * n, "delta_scan")
+    _done(_delta().alofa_delta_scan(_dev(y, "y", f32), _dev(v, "v", f32), v.shape[1], v_off, _dev(kn, "kn", f32), _dev(qn, "qn", f32), _dev(kq, "kq", f32), _dev(g, "g", f32),
+                                    _dev(beta, "beta", f32), state.data_ptr(), state.stride(0), _dev(q_start, "q_start", i32), _dev(state_slots, "state_slots", i32),
+                                    rows, n_seqs, heads, groups, n, p, spread, _stream()), "delta_scan", f"heads={heads} groups={groups} n={n} p={p}")

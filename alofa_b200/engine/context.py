@@ -122,6 +122,10 @@ class StepContext:
         # Small decode steps keep the stream as base + fixed-point accumulator (see open_stream)
         self.stream_acc = None  # int64 [2, rows, hidden], given by the step runner; both zero between steps
         self._stream = None
+        # Several copies of the residual stream (blocks that keep them): fp32 [S, tokens, hidden], and the write a
+        # sublayer left owed, (y, out weights, mix weights), which the next reader of the streams does
+        self.streams = None
+        self.streams_owed = None
 
     # -- the residual stream ---------------------------------------------------------------------
     # A product that adds into the stream may leave its split sums for the next reader to add
@@ -223,6 +227,28 @@ class StepContext:
             for i in sorted(self._stream["unclean"]):
                 self._stream["acc"][i].zero_()
             self._stream["unclean"].clear()
+
+    # -- several residual streams ---------------------------------------------------------------
+    def open_streams(self, h, copies: int) -> None:
+        """Called by the model once the embedding output ``h`` exists: every
+        copy starts equal to it.  One copy is ``h`` itself."""
+        from ..csrc import ops
+
+        self.streams_owed = None
+        if copies <= 1:
+            self.streams = h.view(1, *h.shape)
+            return
+        self.streams = self.buf((copies, *h.shape), torch.float32)
+        ops.streams_fill(self.streams, h)
+
+    def sum_streams(self, h) -> None:
+        """``h`` = the streams' sum, after the write that is still owed."""
+        from ..csrc import ops
+
+        owed, self.streams_owed = self.streams_owed, None
+        if owed is None and self.streams.shape[0] == 1:
+            return  # one copy, nothing owed: h is it
+        ops.hyper_connect(self.streams, owed[0] if owed else None, owed[2] if owed else None, owed[1] if owed else None, sum_out=h)
 
     def host_field(self, name: str) -> np.ndarray:
         at, count = self.layout.fields[name]

@@ -9,13 +9,20 @@ W [h; e]`` with ``e`` the embedding output of the step's tokens.
 ``x = norm(h); h += mixer(x) + feed_forward(x)`` (the feed-forward may be
 absent).  ``embedding_add``: no sublayers, ``h += e``.
 
+``hyper_residual``: several copies of the stream side by side; a sublayer reads
+a weighted sum of them and its output is written back into all of them while
+they are mixed among themselves (see :class:`HyperResidual`).
+
 ``prenorm_residual``: ``h += mixer(norm_a(h)); h += feed_forward(norm_b(h))``
 (src/alofa/model/arch/qwen.mojo:1367-1372, 1418-1510).  The residual stream
 ``h`` is fp32; the parts add into it."""
 from __future__ import annotations
 
+import torch
+
 from ..csrc import ops
-from .base import Part, TensorSpec, build_part, register_part
+from ..errors import AlofaError
+from .base import Part, TensorSpec, as_float32_vector, build_part, register_part
 from .linear import STORE, Linear
 
 
@@ -232,6 +239,102 @@ class EmbeddingAdd(Part):
         ops.add_rows(h, ctx.embedding_output)
 
 
+class HyperResidual(Part):
+    """Pre-norm sublayers over ``streams`` copies x_1 .. x_S of the residual
+    stream (all equal to the embedding output at the start; the model's output
+    is their sum).  Sublayer q (1: the mixer, 2: the feed-forward, which may be
+    absent) reads ``u = sum_s in[s] x_s``, computes ``y = f(norm(u))``, and
+    then every stream moves at once from the old ones: ``x_t <- sum_s mix[s,
+    t] x_s + out[t] y``.  Tensors ``<prefix>hc<q>.in`` [S], ``.out`` [S],
+    ``.mix`` [S, S] (from, to).  With ``connections`` False there are no such
+    tensors and one stream: the plain ``x += f(norm(x))``.
+
+    The streams live in ``ctx.streams`` [S, T, W] fp32 (the model makes them:
+    ``stream_copies`` says how many).  A sublayer's write is left owed
+    (``ctx.streams_owed``) and done by the kernel that reads the streams next:
+    the next sublayer's read and norm, or the sum at the model's end."""
+
+    family = "block"
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.width = int(self.param("hidden_size"))
+        self.connections = bool(self.params.get("connections", True))
+        self.stream_copies = int(self.param("streams")) if self.connections else 1
+        if not 1 <= self.stream_copies <= ops.HYPER_MAX_STREAMS:
+            raise AlofaError("unsupported", "the number of residual streams must lie in [1, 8]", f"streams={self.stream_copies}")
+        self.mixer = build_part("mixer", self.param("mixer"), rt)
+        self.mixer_norm = build_part("norm", self.param("mixer_norm"), rt)
+        ff = self.params.get("feed_forward")
+        self.feed_forward = build_part("feed_forward", ff, rt) if ff is not None else None
+        self.feed_forward_norm = build_part("norm", self.param("feed_forward_norm"), rt) if ff is not None else None
+        for part in (self.mixer, self.feed_forward):
+            if part is not None and not getattr(part, "stores_output", False):
+                raise AlofaError("unsupported", "a sublayer over several streams must be able to store its output", f"kind={part.spec.kind}")
+        self.weights = {}
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None)
+
+    def _numbers(self):
+        return (1, 2) if self.feed_forward is not None else (1,)
+
+    def tensors(self):
+        out = {}
+        for part in self.parts():
+            out.update(part.tensors())
+        if self.connections:
+            S = self.stream_copies
+            for q in self._numbers():
+                pre = f"{self.prefix}hc{q}."
+                out[pre + "in"] = TensorSpec((S,), "ones")
+                out[pre + "out"] = TensorSpec((S,), "ones")
+                out[pre + "mix"] = TensorSpec((S, S), "ones")
+        return out
+
+    def load(self, state):
+        for part in self.parts():
+            part.load(state)
+        dev = self.mixer_norm.weight.device
+        for q in self._numbers():
+            if self.connections:
+                pre = f"{self.prefix}hc{q}."
+                self.weights[q] = tuple(as_float32_vector(state[pre + n]) for n in ("in", "out", "mix"))
+            else:
+                self.weights[q] = (torch.ones(1, device=dev), torch.ones(1, device=dev), torch.ones((1, 1), device=dev))
+
+    @property
+    def graph_safe(self):
+        return all(part.graph_safe for part in self.parts())
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def scratch_row_bytes(self) -> int:
+        return 12 * self.width + sum(getattr(part, "scratch_row_bytes", lambda: 0)() for part in self.parts())
+
+    def _sublayer(self, ctx, q, norm, part, *args):
+        w_in, w_out, w_mix = self.weights[q]
+        hs = ctx.streams
+        n = hs.shape[1]
+        x = ctx.buf((n, self.width), self.rt.dtype)
+        owed = ctx.streams_owed
+        ctx.streams_owed = None
+        # the write the sublayer before left owed, this one's read and its norm: one pass over the streams
+        ops.hyper_connect(hs, owed[0] if owed else None, owed[2] if owed else None, owed[1] if owed else None, w_in, norm.weight, norm.eps, x_out=x)
+        y = ctx.buf((n, self.width), torch.float32)
+        part.forward(ctx, x, y, *args, store=True)
+        ctx.streams_owed = (y, w_out, w_mix)
+
+    def forward(self, ctx, h, cache, writes=True):
+        if ctx.streams is None or ctx.streams.shape[0] != self.stream_copies:
+            raise AlofaError("state", "the step has no residual streams of this block's number", f"streams={self.stream_copies}")
+        self._sublayer(ctx, 1, self.mixer_norm, self.mixer, cache, writes)
+        if self.feed_forward is not None:
+            self._sublayer(ctx, 2, self.feed_forward_norm, self.feed_forward)
+
+
+register_part("block", "hyper_residual", HyperResidual)
 register_part("block", "prenorm_residual", PrenormResidual)
 register_part("block", "parallel_residual", ParallelResidual)
 register_part("block", "embedding_add", EmbeddingAdd)

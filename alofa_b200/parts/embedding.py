@@ -8,7 +8,8 @@ same angle (frequencies made in float64 and rounded to fp32 once, the angle an
 fp32 product, precise sine and cosine).  The head multiplies the normed
 rows whose logits are wanted by ``lm_head.weight`` if the file has it, else by
 the embedding when the two are tied (qwen.mojo:1077-1089, 1512-1523); a tied
-head shares the embedding's memory."""
+head shares the embedding's memory.  With ``scale`` the logits are multiplied
+by it."""
 from __future__ import annotations
 
 import torch
@@ -61,9 +62,12 @@ class LinearHead(Part):
         self.hidden = int(self.param("hidden_size"))
         self.tied_to = self.params.get("tied_to")
         self.name = self.prefix + str(self.params.get("weight_name", "weight"))
+        self.scale = self.params.get("scale")  # the logits are multiplied by this (None: by nothing)
         self.linear = None
 
     def tensors(self):
+        if self.tied_to is not None and self.tied_to == self.name:
+            return {}  # the embedding's own tensor, which the embedding lists
         return {self.name: TensorSpec((self.vocab, self.hidden), optional=self.tied_to is not None)}
 
     def load(self, state):
@@ -79,6 +83,8 @@ class LinearHead(Part):
     def forward(self, ctx, x):
         logits = ctx.buf((x.shape[0], self.vocab), torch.float32)
         self.linear(logits, x, buf=ctx.buf)
+        if self.scale is not None and float(self.scale) != 1.0:
+            ops.scale_rows(logits, float(self.scale))
         return logits
 
 register_part("embedding", "token_embedding", TokenEmbedding)

@@ -14,7 +14,13 @@ unrotated query is carried into the latent space once (``Wuk_h^T q_h``, a
 product per head) so that every head attends to the same cached rows, whose
 first kv_rank numbers also serve as the value; ``Wuv_h`` is applied to the
 attention output of the head.  Both per-head products are one batched launch.
-The stacked ``[Wdq; Wdkv]`` makes both down-projections one product."""
+The stacked ``[Wdq; Wdkv]`` makes both down-projections one product.
+
+Options: ``q_rank`` 0 or absent: no query latent, ``q = x Wq^T`` (tensor
+``q``) and the down-projection is ``Wdkv`` alone; ``gate``: head h's output is
+multiplied by ``sigmoid(x Wg^T)_h`` (tensor ``g`` [heads, hidden], stacked
+under the down-projection); the position part may pair halves and carry a
+magnitude (:class:`~alofa_b200.parts.position.RotaryInterleaved`)."""
 from __future__ import annotations
 
 import torch
@@ -43,7 +49,8 @@ class LatentAttention(Part):
         self.rot = int(p("rot_dim", 0) or 0)
         self.vdim = int(p("vdim"))
         self.kv_rank = int(p("kv_rank"))
-        self.q_rank = int(p("q_rank"))
+        self.q_rank = int(self.params.get("q_rank") or 0)  # 0: queries come straight from x
+        self.gate = bool(self.params.get("gate", False))
         self.scale = float(p("scale"))
         self.eps = float(p("eps"))
         self.has_sink = bool(p("sink", False))
@@ -52,6 +59,8 @@ class LatentAttention(Part):
             raise AlofaError("unsupported", "latent attention wants a head of at least one dimension and a latent of at most 1024", f"dim={self.dim} rot={self.rot} kv_rank={self.kv_rank}")
         self.position = build_part("position", p("position"), rt)
         self.rot_dims = int(getattr(self.position, "dims", 0))
+        self.halves = bool(getattr(self.position, "halves", False))
+        self.magnitude = float(getattr(self.position, "magnitude", 1.0))
         if self.rot_dims > self.rot:
             raise AlofaError("invalid_argument", "more rotated dimensions than the rotated part has", f"dims={self.rot_dims} rot_dim={self.rot}")
         self.width = self.kv_rank + self.rot  # a cache row
@@ -62,20 +71,24 @@ class LatentAttention(Part):
 
     def scratch_row_bytes(self) -> int:
         h = self.heads
-        return 4 * (self.q_rank + self.width) + 4 * self.q_rank + 4 * h * (self.dim + self.rot) + 4 * h * self.width + 4 * h * self.kv_rank + 4 * h * self.vdim + 4 * self.hidden
+        return 4 * (self.q_rank + self.width + h) + 4 * self.q_rank + 4 * h * (self.dim + self.rot) + 4 * h * self.width + 4 * h * self.kv_rank + 4 * h * self.vdim + 4 * self.hidden
 
     def tensors(self):
         pre, h = self.prefix, self.heads
         t = {
-            pre + "dq": TensorSpec((self.q_rank, self.hidden)),
-            pre + "dq.norm": TensorSpec((self.q_rank,), "ones"),
-            pre + "uq": TensorSpec((h * (self.dim + self.rot), self.q_rank)),
             pre + "dkv": TensorSpec((self.width, self.hidden)),
             pre + "dkv.norm": TensorSpec((self.kv_rank,), "ones"),
             pre + "uk": TensorSpec((h * self.dim, self.kv_rank)),
             pre + "uv": TensorSpec((h * self.vdim, self.kv_rank)),
             pre + "o": TensorSpec((self.hidden, h * self.vdim)),
         }
+        if self.q_rank:
+            t.update({pre + "dq": TensorSpec((self.q_rank, self.hidden)), pre + "dq.norm": TensorSpec((self.q_rank,), "ones"),
+                      pre + "uq": TensorSpec((h * (self.dim + self.rot), self.q_rank))})
+        else:
+            t[pre + "q"] = TensorSpec((h * (self.dim + self.rot), self.hidden))
+        if self.gate:
+            t[pre + "g"] = TensorSpec((h, self.hidden))
         if self.has_sink:
             t[pre + "sink"] = TensorSpec((h,))
         t.update(self.position.tensors())
@@ -83,10 +96,12 @@ class LatentAttention(Part):
 
     def load(self, state):
         pre, h = self.prefix, self.heads
-        self.down = Linear(torch.cat([state[pre + "dq"], state[pre + "dkv"]], dim=0), None, STORE)
-        self.q_norm = as_float32_vector(state[pre + "dq.norm"])
+        # one product for everything that leaves fp32 sums: [Wdq; Wdkv; Wg]
+        stacked = ([state[pre + "dq"]] if self.q_rank else []) + [state[pre + "dkv"]] + ([state[pre + "g"]] if self.gate else [])
+        self.down = Linear(torch.cat(stacked, dim=0), None, STORE)
+        self.q_norm = as_float32_vector(state[pre + "dq.norm"]) if self.q_rank else None
         self.kv_norm = as_float32_vector(state[pre + "dkv.norm"])
-        self.up_q = Linear(state[pre + "uq"], None, STORE)
+        self.up_q = Linear(state[pre + "uq"] if self.q_rank else state[pre + "q"], None, STORE)
         # [heads, kv_rank, dim]: row c of head h holds column c of Wuk_h, so the per-head product q_h -> Wuk_h^T q_h reads rows
         self.uk_t = state[pre + "uk"].view(h, self.dim, self.kv_rank).transpose(1, 2).contiguous() if self.dim else None
         self.uv = state[pre + "uv"].contiguous()
@@ -100,15 +115,16 @@ class LatentAttention(Part):
         n, dt, heads = x.shape[0], self.rt.dtype, self.heads
         group = ctx.groups[cache.group]
         freq = self.position.frequencies()
-        lat = ctx.buf((n, self.q_rank + self.width), torch.float32)
+        gate_at = self.q_rank + self.width
+        lat = ctx.buf((n, gate_at + (heads if self.gate else 0)), torch.float32)
         self.down(lat, x, buf=ctx.buf)
-        cq = ctx.buf((n, self.q_rank), dt)
+        cq = ctx.buf((n, self.q_rank), dt) if self.q_rank else None
         ops.latent_prepare(cq, cache.k if writes else None, lat, self.q_norm, self.kv_norm, freq, ctx.positions, group.slot_map,
-                           self.q_rank, self.kv_rank, self.rot, self.rot_dims, self.eps)
+                           self.q_rank, self.kv_rank, self.rot, self.rot_dims, self.eps, self.halves, self.magnitude)
         q = ctx.buf((n, heads * (self.dim + self.rot)), dt)
-        self.up_q(q, cq, buf=ctx.buf)
+        self.up_q(q, cq if self.q_rank else x, buf=ctx.buf)
         qa = ctx.buf((n, heads * self.width), dt)
-        ops.latent_query_turn(qa, q, freq, ctx.positions, heads, self.dim, self.rot, self.rot_dims, self.kv_rank)
+        ops.latent_query_turn(qa, q, freq, ctx.positions, heads, self.dim, self.rot, self.rot_dims, self.kv_rank, self.halves, self.magnitude)
         if self.dim:
             # per head: qa[:, h, :kv_rank] = q[:, h, :dim] Wuk_h
             ops.gemm_batched(qa, q, self.uk_t, heads, n, self.kv_rank, self.dim, heads * (self.dim + self.rot), self.dim + self.rot,
@@ -121,6 +137,8 @@ class LatentAttention(Part):
         # per head: o[:, h] = o_lat[:, h] Wuv_h^T
         ops.gemm_batched(o, o_lat, self.uv, heads, n, self.vdim, self.kv_rank, heads * self.kv_rank, self.kv_rank, self.kv_rank, self.vdim * self.kv_rank,
                          heads * self.vdim, self.vdim)
+        if self.gate:
+            ops.head_gate(o, lat, gate_at, heads, self.vdim)
         if store:
             self.out(h, o, buf=ctx.buf)
         else:

@@ -10,6 +10,8 @@ import numpy as np
 import torch
 
 from ..config.spec import ModelSpec
+from ..csrc import ops
+from ..errors import AlofaError
 from .base import Runtime, build_part
 
 
@@ -25,6 +27,11 @@ class Model:
         self.run = [(e.layer, i if e.cache is None else e.cache) for i, e in enumerate(spec.run)]
         # a block may read the embedding output of the step's tokens later on (ctx.embedding_output)
         self.keeps_embedding = any(getattr(block, "needs_embedding_output", False) for block in self.layers)
+        # blocks that keep several copies of the residual stream say how many (ctx.streams); every block of a model says the same
+        copies = {int(getattr(block, "stream_copies", 0)) for block in self.layers}
+        if len(copies) > 1:
+            raise AlofaError("unsupported", "blocks over several residual streams cannot be mixed with others", f"stream_copies={sorted(copies)}")
+        self.stream_copies = copies.pop() if copies else 0
 
     def parts(self):
         return [self.embedding, *self.layers, self.final_norm, self.head]
@@ -49,7 +56,7 @@ class Model:
         layer that needs most): what the step runner sizes its arena from."""
         hidden = self.spec.hidden_size
         per_layer = max([getattr(block, "scratch_row_bytes", lambda: 0)() for block in self.layers] + [8 * hidden])
-        return 4 * hidden + 4 * hidden + (4 * hidden if self.keeps_embedding else 0), per_layer
+        return 4 * hidden + 4 * hidden + (4 * hidden if self.keeps_embedding else 0) + (4 * hidden * self.stream_copies if self.stream_copies > 1 else 0), per_layer
 
     def cache_plan(self) -> dict:
         """run index -> cache spec, for the entries that own a cache."""
@@ -64,6 +71,8 @@ class Model:
         if self.keeps_embedding:
             ctx.embedding_output = ctx.buf(tuple(h.shape), torch.float32)
             ctx.embedding_output.copy_(h)
+        if self.stream_copies:
+            ctx.open_streams(h, self.stream_copies)
         for i, (layer, cache) in enumerate(self.run):
             block = self.layers[layer]
             if not getattr(block, "absorbs_pending", False):
@@ -71,6 +80,8 @@ class Model:
             ctx.begin_layer()
             block.forward(ctx, h, caches.get(cache), writes=(cache == i))
         ctx.end_layers()
+        if self.stream_copies:
+            ctx.sum_streams(h)
         if ctx.n_out == 0:  # a prompt portion whose logits nobody wants
             ctx.close_stream()
             return None

@@ -9,6 +9,8 @@ rotation itself, ``y[d] = a cos - b sin``, ``y[d + rot/2] = b cos + a sin``
 rotate-and-store kernel, which reads the table built here."""
 from __future__ import annotations
 
+import math
+
 import numpy as np
 import torch
 
@@ -60,7 +62,16 @@ class RotaryInterleaved(Part):
     < dims / 2; at position p the pair (u, v) becomes (u cos a - v sin a, v cos
     a + u sin a) with a = p * f_i, f_i = base^(-2i / dims).  f_i is rounded to
     fp32 once (from the power in f64); position, angle, cosine and sine are
-    fp32 in the kernels that turn, so no table and no longest position."""
+    fp32 in the kernels that turn, so no table and no longest position.
+
+    ``layout`` "halves" pairs dimension i with i + dims / 2 instead (kernels
+    that take a ``halves`` flag; :meth:`apply` does neighbouring pairs only).
+    ``scaling`` = ``{factor, original, fast, slow}`` stretches the slow
+    frequencies (YaRN): with ``turns(t) = dims * ln(original / (2 pi t)) / (2 ln
+    base)``, ``lo = max(floor(turns(fast)), 0)``, ``hi = min(ceil(turns(slow)),
+    dims - 1)`` and ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` the
+    frequency is ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``, and cosine and
+    sine are multiplied by ``magnitude = 0.1 * ln(factor) + 1``."""
 
     family = "position"
     graph_safe = True
@@ -69,19 +80,46 @@ class RotaryInterleaved(Part):
         super().__init__(spec, rt)
         self.dims = int(self.param("dims"))
         self.base = float(self.param("base"))
-        if self.dims < 0 or self.dims % 2 or self.base <= 0:
-            raise AlofaError("unsupported", "rotary dims must be even and the base positive", f"dims={self.dims} base={self.base}")
+        self.layout = str(self.params.get("layout", "pairs"))
+        self.scaling = self.params.get("scaling")
+        if self.dims < 0 or self.dims % 2 or self.base <= 0 or self.layout not in ("pairs", "halves"):
+            raise AlofaError("unsupported", "rotary dims must be even, the base positive, the layout 'pairs' or 'halves'", f"dims={self.dims} base={self.base} layout={self.layout}")
+        self.magnitude = 1.0
+        if self.scaling:
+            sc = {k: float(self.scaling[k]) for k in ("factor", "original", "fast", "slow")}
+            if min(sc.values()) <= 0 or self.base == 1.0:
+                raise AlofaError("invalid_argument", "rotary scaling wants positive numbers and a base other than 1", f"scaling={self.scaling}")
+            self.scaling = sc
+            self.magnitude = 0.1 * math.log(sc["factor"]) + 1.0
         self._freq = None
 
+    @property
+    def halves(self) -> bool:
+        return self.layout == "halves"
+
     def key(self):
-        return ("rotary_interleaved", self.dims, self.base)
+        return ("rotary_interleaved", self.dims, self.base, tuple(sorted(self.scaling.items())) if self.scaling else None)
+
+    def make_frequencies(self) -> np.ndarray:
+        """f_i, i < dims / 2, in float64 (rounded to fp32 once, by the caller)."""
+        i = np.arange(max(self.dims // 2, 1), dtype=np.float64)
+        freq = np.power(np.float64(self.base), -2.0 * i / max(self.dims, 1))
+        if self.scaling:
+            sc = self.scaling
+
+            def turns(t):
+                return self.dims * math.log(sc["original"] / (2.0 * math.pi * t)) / (2.0 * math.log(self.base))
+
+            lo = max(math.floor(turns(sc["fast"])), 0)
+            hi = min(math.ceil(turns(sc["slow"])), self.dims - 1)
+            ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            freq = freq / sc["factor"] * ramp + freq * (1.0 - ramp)
+        return freq
 
     def load(self, state):
         tables = state.setdefault("__rotary_tables__", {})
         if self.key() not in tables:
-            i = np.arange(max(self.dims // 2, 1), dtype=np.float64)
-            freq = np.power(np.float64(self.base), -2.0 * i / max(self.dims, 1)).astype(np.float32)
-            tables[self.key()] = torch.from_numpy(freq).to(self.rt.device)
+            tables[self.key()] = torch.from_numpy(self.make_frequencies().astype(np.float32)).to(self.rt.device)
         self._freq = tables[self.key()]
 
     def frequencies(self) -> torch.Tensor:
@@ -94,6 +132,9 @@ class RotaryInterleaved(Part):
     def apply(self, ctx, q, k):
         """Turn q [T, heads, hd] and k [T, kv_heads, hd] (views) in place."""
         from ..csrc import ops
+
+        if self.halves or self.magnitude != 1.0:
+            raise AlofaError("unsupported", "apply() turns neighbouring pairs without a magnitude only", f"layout={self.layout} magnitude={self.magnitude}")
 
         ops.rotary_interleaved(q, self._freq, ctx.positions, q.shape[1], q.shape[2], self.dims)
         if k.shape[1]:

@@ -22,7 +22,21 @@ B_t``, ``q_t = C_t``, ``y_t += D x_t``; then ``y * silu(z)``, an RMS norm in
 ``gated_linear_attention``: ``q = W_q h / sqrt(dim)``, ``k = W_k h``, ``v = W_v
 h``; ``a_t = sigmoid(W_a2 (W_a1 h) + b)^(1/tau)`` per key channel; each head's
 output is RMS-normed over its value channels with one weight shared by the
-heads, the heads are concatenated, multiplied by ``silu(W_g h)`` and projected."""
+heads, the heads are concatenated, multiplied by ``silu(W_g h)`` and projected.
+
+``min_gru``: a recurrence element by element whose gates read the current
+token only: ``z = sigmoid(W_z h + b_z)``, ``x = W_x h + b_x``, the candidate ``x
++ 1/2`` where ``x >= 0`` and ``sigmoid(x)`` below, ``S_t = (1 - z) S_(t-1) + z
+* candidate``; the output is ``W_o (S_t * silu(W_g h))``.
+
+``gated_delta``: the gated delta rule over a matrix state per head with one
+decay per head and key channel, ``S <- diag(g_t) S; u = beta_t (v_t - S^T
+k_t); S <- S + k_t u^T; o_t = S^T q_t``; q, k and v each pass a short causal
+convolution per channel (no bias) and silu, q and k are made unit vectors per
+head (q also times ``dim^(-1/2)``), ``beta = sigmoid(W_b h)``, ``g =
+exp(-exp(A_log) * softplus(W_a2 (W_a1 h) + dt_bias))``; every head's output is
+RMS-normed over its value channels with one weight shared by the heads and
+multiplied by ``sigmoid(W_g2 (W_g1 h))``, then projected."""
 from __future__ import annotations
 
 import torch
@@ -179,5 +193,132 @@ class GatedLinearAttention(Part):
         _project_out(ctx, self.out_add, self.out_store, h, normed, store)
 
 
+class MinGRU(Part):
+    family = "mixer"
+    graph_safe = True
+    stores_output = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.hidden, self.width = int(self.param("hidden_size")), int(self.param("width"))
+        if self.width <= 0:
+            raise AlofaError("invalid_argument", "the recurrence's width must be positive", f"params={self.params}")
+
+    def cache_spec(self):
+        return SlotState((self.width,), torch.float32)
+
+    def scratch_row_bytes(self) -> int:
+        return 4 * 3 * self.width + 4 * self.width + 8 * self.hidden
+
+    def tensors(self):
+        pre = self.prefix
+        return {pre + "z": TensorSpec((self.width, self.hidden)), pre + "z.b": TensorSpec((self.width,)), pre + "x": TensorSpec((self.width, self.hidden)),
+                pre + "x.b": TensorSpec((self.width,)), pre + "g": TensorSpec((self.width, self.hidden)), pre + "o": TensorSpec((self.hidden, self.width))}
+
+    def load(self, state):
+        pre = self.prefix
+        bias = torch.cat([as_float32_vector(state[pre + "z.b"]), as_float32_vector(state[pre + "x.b"]), torch.zeros(self.width, dtype=torch.float32, device=state[pre + "g"].device)])
+        self.w_in = Linear(torch.cat([state[pre + n] for n in ("z", "x", "g")], dim=0), bias, STORE)  # [z | x | g]
+        self.out_add = Linear(state[pre + "o"], None, RESIDUAL)
+        self.out_store = Linear(state[pre + "o"], None, STORE)
+
+    def forward(self, ctx, x, h, cache, writes=True, store=False):
+        n, w = x.shape[0], self.width
+        u = ctx.buf((n, 3 * w), torch.float32)  # the projections' fp32 sums, biases added
+        self.w_in(u, x, buf=ctx.buf)
+        y = ctx.buf((n, w), self.rt.dtype)
+        ops.min_gru(y, u, 0, w, 2 * w, cache.state, ctx.q_start, ctx.state_slots, ctx.n_seqs)
+        _project_out(ctx, self.out_add, self.out_store, h, y, store)
+
+
+class GatedDelta(Part):
+    family = "mixer"
+    graph_safe = True
+    stores_output = True
+
+    UNIT_EPS = 1e-6  # inside the root of the unit norms of q and k
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = self.param
+        self.hidden = int(p("hidden_size"))
+        self.heads, self.kv_heads, self.dim, self.vdim = int(p("heads")), int(p("kv_heads")), int(p("dim")), int(p("vdim"))
+        self.taps, self.eps = int(p("conv")), float(p("eps"))
+        if min(self.heads, self.kv_heads, self.dim, self.vdim, self.taps) <= 0 or self.heads % self.kv_heads:
+            raise AlofaError("invalid_argument", "delta-rule sizes must be positive and kv_heads must divide heads", f"params={self.params}")
+        if self.dim > 1024:
+            raise AlofaError("unsupported", "the recurrence kernel holds at most 1,024 key channels a head", f"dim={self.dim}")
+        self.qk, self.v = self.kv_heads * self.dim, self.heads * self.vdim
+        self.decays = self.heads * self.dim
+        self.channels = 2 * self.qk + self.v  # what passes the convolution: q, k, v
+        self.in_rows = self.channels + self.heads  # [q | k | v | beta]
+        self.scan_words = self.heads * self.vdim * self.dim
+        self.conv_words = (self.taps - 1) * self.channels
+        self.rank_a = self.rank_g = None  # the inner sizes of the decays' and the gate's projections, from the tensors
+
+    def cache_spec(self):
+        # one fp32 vector per request: the state [head][value][key], then the convolution's last inputs
+        return SlotState((self.scan_words + self.conv_words,), torch.float32)
+
+    def scratch_row_bytes(self) -> int:
+        return 4 * (self.in_rows + self.channels + 2 * (self.decays + self.v) + 2 * self.qk + 2 * self.heads + self.kv_heads + 2 * self.v) + 8 * self.hidden + 512
+
+    def tensors(self):
+        pre = self.prefix
+        ra, rg = -int(self.params.get("decay_rank") or 16), -int(self.params.get("gate_rank") or 16)  # the files' own; these for random weights
+        return {
+            pre + "q": TensorSpec((self.qk, self.hidden)), pre + "q.conv": TensorSpec((self.qk, self.taps)),
+            pre + "k": TensorSpec((self.qk, self.hidden)), pre + "k.conv": TensorSpec((self.qk, self.taps)),
+            pre + "v": TensorSpec((self.v, self.hidden)), pre + "v.conv": TensorSpec((self.v, self.taps)),
+            pre + "b": TensorSpec((self.heads, self.hidden)), pre + "A_log": TensorSpec((self.heads,)), pre + "norm": TensorSpec((self.vdim,), "ones"),
+            pre + "a1": TensorSpec((ra, self.hidden)), pre + "a2": TensorSpec((self.decays, ra)), pre + "dt_bias": TensorSpec((self.decays,)),
+            pre + "g1": TensorSpec((rg, self.hidden)), pre + "g2": TensorSpec((self.v, rg)), pre + "o": TensorSpec((self.hidden, self.v)),
+        }
+
+    def load(self, state):
+        pre = self.prefix
+        self.w_in = Linear(torch.cat([state[pre + n] for n in ("q", "k", "v", "b")], dim=0), None, STORE)
+        self.conv_w = torch.cat([state[pre + n + ".conv"] for n in ("q", "k", "v")], dim=0).to(torch.float32).contiguous()
+        a1, a2, g1, g2 = (state[pre + n] for n in ("a1", "a2", "g1", "g2"))
+        self.rank_a, self.rank_g = a1.shape[0], g1.shape[0]
+        if a2.shape[1] != self.rank_a or g2.shape[1] != self.rank_g:
+            raise AlofaError("invalid_argument", "the two halves of a low-rank projection disagree about their inner size",
+                             f"a1={tuple(a1.shape)} a2={tuple(a2.shape)} g1={tuple(g1.shape)} g2={tuple(g2.shape)}")
+        # both low-rank maps as two products: [a1; g1], then the second halves on the diagonal of one matrix (its zero blocks add exact zeros)
+        self.low = Linear(torch.cat([a1, g1], dim=0), None, STORE)
+        second = torch.zeros((self.decays + self.v, self.rank_a + self.rank_g), dtype=a2.dtype, device=a2.device)
+        second[: self.decays, : self.rank_a] = a2
+        second[self.decays :, self.rank_a :] = g2
+        self.high = Linear(second, None, STORE)
+        self.dt_bias = as_float32_vector(state[pre + "dt_bias"])
+        self.a_log = as_float32_vector(state[pre + "A_log"])
+        self.norm_w = as_float32_vector(state[pre + "norm"])
+        self.out_add = Linear(state[pre + "o"], None, RESIDUAL)
+        self.out_store = Linear(state[pre + "o"], None, STORE)
+
+    def forward(self, ctx, x, h, cache, writes=True, store=False):
+        n, f32 = x.shape[0], torch.float32
+        H, G, N, P = self.heads, self.kv_heads, self.dim, self.vdim
+        u = ctx.buf((n, self.in_rows), f32)  # [q | k | v | beta], the projection's fp32 sums
+        self.w_in(u, x, buf=ctx.buf)
+        low = ctx.buf((n, self.rank_a + self.rank_g), self.rt.dtype)
+        self.low(low, x, buf=ctx.buf)
+        z = ctx.buf((n, self.decays + self.v), f32)  # the decays' logits, then the output gate's
+        self.high(z, low, buf=ctx.buf)
+        st = cache.state
+        xc = ctx.buf((n, self.channels), f32)
+        ops.causal_conv(xc, u, 0, self.conv_w, None, st[:, self.scan_words:], ctx.q_start, ctx.state_slots, ctx.seq_of_token, ctx.n_seqs)
+        qn, kn = ctx.buf((n, self.qk), f32), ctx.buf((n, self.qk), f32)
+        kq, g, beta = ctx.buf((n, G), f32), ctx.buf((n, self.decays), f32), ctx.buf((n, H), f32)
+        ops.delta_prepare(qn, kn, kq, g, beta, xc, z, u, self.channels, self.dt_bias, self.a_log, H, G, N, self.UNIT_EPS, N ** -0.5)
+        y = ctx.buf((n, self.v), f32)
+        ops.delta_scan(y, xc, 2 * self.qk, kn, qn, kq, g, beta, st, ctx.q_start, ctx.state_slots, ctx.n_seqs, H, G, N, P, spread=SCAN_SPREAD)
+        normed = ctx.buf((n, self.v), self.rt.dtype)
+        ops.gated_group_norm(normed, y, z, self.decays, self.norm_w, H, self.eps, gate_first=False, sigmoid=True)
+        _project_out(ctx, self.out_add, self.out_store, h, normed, store)
+
+
+register_part("mixer", "min_gru", MinGRU)
+register_part("mixer", "gated_delta", GatedDelta)
 register_part("mixer", "state_space", StateSpaceMixer)
 register_part("mixer", "gated_linear_attention", GatedLinearAttention)
