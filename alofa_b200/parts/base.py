@@ -39,7 +39,7 @@ _REGISTRY: dict = {f: {} for f in FAMILIES}
 @dataclass
 class TensorSpec:
     """A tensor a part expects under its name: shape, the law random weights
-    are drawn from ("normal": N(0, 0.02); "ones": 1 + N(0, 0.01)), and whether
+    are drawn from ("normal": N(0, 0.02); "ones": 1 + N(0, 0.01); "identity": I + N(0, 0.01)), and whether
     the file may leave it out.  A negative entry of ``shape`` is a size that
     the file decides; random weights use its magnitude."""
 

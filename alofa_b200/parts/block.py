@@ -289,7 +289,7 @@ class HyperResidual(Part):
                 pre = f"{self.prefix}hc{q}."
                 out[pre + "in"] = TensorSpec((S,), "ones")
                 out[pre + "out"] = TensorSpec((S,), "ones")
-                out[pre + "mix"] = TensorSpec((S, S), "ones")
+                out[pre + "mix"] = TensorSpec((S, S), "identity")
         return out
 
     def load(self, state):

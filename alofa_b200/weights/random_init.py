@@ -1,7 +1,7 @@
 """Random weights from a configuration and a seed.
 
 Matrices and biases are drawn from N(0, 0.02), norm weights from
-1 + N(0, 0.01).  Every tensor has its own generator, seeded from the seed and
+1 + N(0, 0.01), matrices that mix residual streams from I + N(0, 0.01).  Every tensor has its own generator, seeded from the seed and
 the tensor's name, so a tensor's values do not depend on which other tensors
 exist or in which order they are made.  The reference has no such mode (its
 tests use the real checkpoint or no model at all)."""
@@ -31,6 +31,8 @@ def random_tensor(seed: int, name: str, shape, init: str, dtype, device="cpu") -
         x.mul_(0.02)
     elif init == "ones":
         x.mul_(0.01).add_(1.0)
+    elif init == "identity":  # a square matrix near the identity: what it mixes neither grows nor dies out layer after layer
+        x.mul_(0.01).add_(torch.eye(x.shape[0], x.shape[1], dtype=torch.float32, device=device))
     else:
         raise AlofaError("invalid_argument", "unknown init law", f"name={name} init={init}")
     return x.to(dtype)

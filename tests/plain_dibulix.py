@@ -130,18 +130,21 @@ def windowed_attention(h, w, p, m):
     return o.reshape(T, H * dv) @ w[p + "o"].T
 
 
-def min_gru(h, w, p):
-    """The right branch of the 'parallel' mixer."""
-    z = sigmoid(h @ w[p + "z"].T + w[p + "z.b"])
-    u = h @ w[p + "x"].T + w[p + "x.b"]
+def min_gru_recurrence(z_logit, u, gate_logit):
+    """All [T, width]: the state after every token, times silu(gate)."""
+    z = sigmoid(z_logit)
     cand = np.where(u >= 0, u + 0.5, sigmoid(u))
-    gate = silu(h @ w[p + "g"].T)
     S = np.zeros(z.shape[1])
     out = np.zeros_like(z)
-    for t in range(h.shape[0]):
+    for t in range(z.shape[0]):
         S = (1.0 - z[t]) * S + z[t] * cand[t]
-        out[t] = S * gate[t]
-    return out @ w[p + "o"].T
+        out[t] = S * silu(gate_logit[t])
+    return out
+
+
+def min_gru(h, w, p):
+    """The right branch of the 'parallel' mixer."""
+    return min_gru_recurrence(h @ w[p + "z"].T + w[p + "z.b"], h @ w[p + "x"].T + w[p + "x.b"], h @ w[p + "g"].T) @ w[p + "o"].T
 
 
 def parallel_mixer(h, w, p, m):
@@ -173,19 +176,28 @@ def delta_rule(q, k, v, beta, g):
     return out
 
 
+def unit_vectors(x):
+    return x / np.sqrt((x * x).sum(-1, keepdims=True) + 1e-6)
+
+
+def channel_decays(logits, dt_bias, a_log):
+    """logits [T, H, d] -> g = exp(-exp(A_log_h) * softplus(logits + dt_bias))."""
+    T, H, d = logits.shape
+    return np.exp(-np.exp(a_log)[None, :, None] * softplus(logits + dt_bias.reshape(1, H, d)))
+
+
 def channel_delta_mixer(h, w, p, m, eps):
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = short_convolution(h @ w[p + "q"].T, w[p + "q.conv"]).reshape(T, G, d)
     k = short_convolution(h @ w[p + "k"].T, w[p + "k.conv"]).reshape(T, G, d)
     v = short_convolution(h @ w[p + "v"].T, w[p + "v.conv"]).reshape(T, H, dv)
-    q = q / np.sqrt((q * q).sum(-1, keepdims=True) + 1e-6) * d ** -0.5
-    k = k / np.sqrt((k * k).sum(-1, keepdims=True) + 1e-6)
+    q = unit_vectors(q) * d ** -0.5
+    k = unit_vectors(k)
     heads_of = np.arange(H) // (H // G)
     q, k = q[:, heads_of], k[:, heads_of]
     beta = sigmoid(h @ w[p + "b"].T)
-    rate = np.exp(w[p + "A_log"])[None, :, None]
-    g = np.exp(-rate * softplus(((h @ w[p + "a1"].T) @ w[p + "a2"].T + w[p + "dt_bias"]).reshape(T, H, d)))
+    g = channel_decays(((h @ w[p + "a1"].T) @ w[p + "a2"].T).reshape(T, H, d), w[p + "dt_bias"], w[p + "A_log"])
     o = delta_rule(q, k, v, beta, g)
     o = o / np.sqrt((o * o).mean(-1, keepdims=True) + eps) * w[p + "norm"][None, None, :]
     o = o * sigmoid((h @ w[p + "g1"].T) @ w[p + "g2"].T).reshape(T, H, dv)
@@ -231,6 +243,22 @@ def mixer(kind, h, w, p, m, eps):
     raise ValueError(kind)
 
 
+def connect(xs, y, w_mix, w_out):
+    """Every stream at once from the old ones: x_t <- sum_s mix[s, t] x_s + out[t] y."""
+    S = len(xs)
+    return [sum(w_mix[s, t] * xs[s] for s in range(S)) + w_out[t] * y for t in range(S)]
+
+
+def greedy(w, cfg, prompt, n_new):
+    """The next ``n_new`` tokens by the largest logit, the whole sequence recomputed for each."""
+    seq, out = list(prompt), []
+    for _ in range(n_new):
+        tok = int(np.argmax(forward(w, cfg, seq)[-1]))
+        out.append(tok)
+        seq.append(tok)
+    return out
+
+
 def forward(w, cfg, ids, layer_outputs=None):
     """Logits [T, vocab] of one whole sequence.  ``layer_outputs`` (a list)
     collects the residual stream after every layer (the streams' sum)."""
@@ -250,7 +278,7 @@ def forward(w, cfg, ids, layer_outputs=None):
             hc = p + f"hc{number}."
             u = sum(w[hc + "in"][s] * xs[s] for s in range(streams))
             y = f(rms_norm(u, w[p + f"norm{number}"], eps))
-            xs = [sum(w[hc + "mix"][s, t] * xs[s] for s in range(streams)) + w[hc + "out"][t] * y for t in range(streams)]
+            xs = connect(xs, y, w[hc + "mix"], w[hc + "out"])
         if layer_outputs is not None:
             layer_outputs.append(sum(xs) if xs is not None else x.copy())
     if xs is not None:
