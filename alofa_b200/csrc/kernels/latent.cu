@@ -348,6 +348,10 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(T* __re
     for (int e = threadIdx.x; e < n_in * D; e += blockDim.x) {
       const int j = e / D, d = e - j * D;
       const int key = c0 + j;
+      if (key < first) {  // before the window: its page may have been given back, and its table entry then names no page
+        rows[j * pitch + d] = 0.f;
+        continue;
+      }
       const int slot = table[key / page_size] * page_size + key % page_size;
       rows[j * pitch + d] = to_f(cache[(size_t)slot * D + d]);
     }

@@ -128,7 +128,7 @@ latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa
     const int j = tid / PER_ROW, c0 = tid - j * PER_ROW;
     bf16* dst = Ks + ((size_t)buf * BN + j) * PITCH;
     const int key = b * BN + j;
-    if (key <= key_hi) {
+    if (key >= key_lo && key <= key_hi) {  // rows before the window may lie in a page that was given back: its table entry names no page
       const int page = key / page_size;
       const bf16* src = cache + ((size_t)table[page] * page_size + (key - page * page_size)) * D;
 #pragma unroll 4

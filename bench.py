@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--shape 0.5b|1.5b|7b] [--no-extra]
     python bench.py --design kotutar [--size 1k|2k]     (another line: that design beside Qwen2 at equal layer sizes)
     python bench.py --design darolix [--size 1k|2k]     (another line: that design beside Kotutar at equal layer sizes)
+    python bench.py --design dibulix [--size 1k|2k]     (another line: that design beside Darolix at equal layer sizes)
 
 The default run has the layer sizes of the Qwen2.5-0.5B shape with random
 weights, a batch of 8 requests with 2,048-token prompts inside a 4,096-token
@@ -510,6 +511,53 @@ def qwen2_config_like(z: dict):
                        intermediate_size=z["ff"], vocab_size=z["vocab"], rms_norm_eps=1e-6, rope_theta=1e4, tie_word_embeddings=False, max_position_embeddings=32768)
 
 
+# --design dibulix: gated-delta-rule, latent-attention and attention + minGRU layers over four residual streams, every layer
+# with a dense feed-forward (squared relu), beside the Darolix design at the same width, layers, heads and vocabulary.  Inner
+# sizes after published models of the kind: the delta rule with keys half and values as wide as the model in heads of 128 x
+# 256 and low-rank maps of 16 for decays and gate; the latent attention of DESIGN_SIZES with a window of 1,024 and stretched
+# frequencies; attention heads of 128 (half of each turned) with a window of 1,024 beside a minGRU twice the model's width.
+DIBULIX_SIZES = {
+    "1k": dict(delta_heads=4, delta_kv_heads=2, delta_dim=128, delta_vdim=256, conv=4, low_rank=16, kv_heads=2, att_dim=128, att_rot=64, window=1024, gru_width=2048, streams=4),
+    "2k": dict(delta_heads=8, delta_kv_heads=4, delta_dim=128, delta_vdim=256, conv=4, low_rank=16, kv_heads=4, att_dim=128, att_rot=64, window=1024, gru_width=4096, streams=4),
+}
+
+
+def dibulix_config(z: dict, b: dict):
+    """Delta-rule, latent-attention, side-by-side and delta-rule layers in turn, every layer with a dense feed-forward."""
+    from alofa_b200.models.dibulix import DeltaConfig, DibulixConfig, DibulixLayer, LatentConfig, ParallelConfig, Rotary, WindowedAttentionConfig
+
+    delta = DeltaConfig(b["delta_heads"], b["delta_kv_heads"], b["delta_dim"], b["delta_vdim"], b["conv"])
+    latent = LatentConfig(z["heads"], z["dim"], z["rot"], z["vdim"], z["kv_rank"], (z["dim"] + z["rot"]) ** -0.5,
+                          Rotary(1e4, z["rot"], {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}), b["window"])
+    pair = ParallelConfig(WindowedAttentionConfig(z["heads"], b["kv_heads"], b["att_dim"], b["att_dim"], b["att_dim"] ** -0.5, Rotary(1e6, b["att_rot"]), b["window"]),
+                          b["gru_width"], 1.0, 1.0)
+    kinds = (("channel_delta", delta), ("latent_attention", latent), ("parallel", pair), ("channel_delta", delta))
+    layers = [DibulixLayer(*kinds[i % 4], z["ff"]) for i in range(z["layers"])]
+    return DibulixConfig(z["vocab"], z["width"], 1e-6, 1.0, b["streams"], layers)
+
+
+def dibulix_numbers(z: dict, b: dict) -> dict:
+    """Bytes a decode step reads and flops a token costs for the Dibulix sizes (bf16 weights and caches, fp32 states).  Both
+    windows are shorter than the bench's prompts, so a decode step reads a window's worth of cache rows per request,
+    whatever the context: that is counted as state, and nothing grows with the context."""
+    w, h = z["width"], z["heads"]
+    qk, v, dec, r = b["delta_kv_heads"] * b["delta_dim"], b["delta_heads"] * b["delta_vdim"], b["delta_heads"] * b["delta_dim"], b["low_rank"]
+    delta = w * (2 * qk + v + b["delta_heads"]) + r * (2 * w + dec + v) + v * w
+    d_row = z["kv_rank"] + z["rot"]
+    latent = w * h * (z["dim"] + z["rot"]) + w * d_row + h * z["dim"] * z["kv_rank"] + h * z["vdim"] * z["kv_rank"] + h * w + h * z["vdim"] * w
+    att = w * (h + 2 * b["kv_heads"]) * b["att_dim"] + h * b["att_dim"] * w
+    gru = 4 * w * b["gru_width"]
+    kinds = [("delta", delta), ("latent", latent), ("pair", att + gru), ("delta", delta)]
+    used = [kinds[i % 4] for i in range(z["layers"])]
+    n = {k: sum(1 for name, _ in used if name == k) for k in ("delta", "latent", "pair")}
+    params = sum(p for _, p in used) + z["layers"] * 2 * w * z["ff"]
+    state_bytes = 4 * (n["delta"] * (dec * b["delta_vdim"] + (b["conv"] - 1) * (2 * qk + v)) + n["pair"] * b["gru_width"])
+    window_bytes = 2 * b["window"] * (n["latent"] * d_row + n["pair"] * 2 * b["kv_heads"] * b["att_dim"])
+    return {"weight_bytes": 2 * (params + z["vocab"] * w), "kv_bytes_per_token": 0, "flops_per_token": 2.0 * params,
+            "attn_flops_per_pair": n["latent"] * 2.0 * h * (d_row + z["kv_rank"]) + n["pair"] * 4.0 * h * b["att_dim"], "head_flops": 2.0 * w * z["vocab"],
+            "state_bytes_per_request": 2 * state_bytes + window_bytes}
+
+
 class KernelClock:
     """Times every kernel call of the package's ops module with its own pair of CUDA events during one
     step (run outright, no graph), and sets each beside the time its own operands allow: the larger of
@@ -517,7 +565,7 @@ class KernelClock:
 
     PRODUCTS = ("gemm_tc", "gemm_generic", "gemm_batched", "gemm_tc_rope")
     ATTENTION = ("attention_bf16", "latent_attention_bf16", "latent_attention", "paged_attention_generic")
-    STATE = ("linear_scan", "causal_conv")  # read and leave a state per request
+    STATE = ("linear_scan", "causal_conv", "delta_scan", "min_gru")  # read and leave a state per request
 
     def __init__(self, peaks: dict):
         self.peaks = peaks
@@ -553,6 +601,27 @@ class KernelClock:
             fp32_rate = _t.cuda.get_device_properties(0).multi_processor_count * 128 * 2 * 1.965e9
             ideal = max(5.0 * rows * heads * n * p / fp32_rate, byts / (self.peaks["hbm_gbs"] * 1e9)) * 1e6
             return ideal, 5.0 * rows * heads * n * p, byts
+        elif name == "delta_scan":
+            # y, v, ., kn, qn, kq, g, beta, state, q_start, slots, n_seqs, heads, groups, n, p: the rows once, the live requests' states read and written
+            y, n_seqs, heads, groups, n, p = args[0], args[11], args[12], args[13], args[14], args[15]
+            rows = y.shape[0]
+            byts = 4 * rows * (2 * heads * p + 2 * groups * n + heads * n + heads + groups) + 8 * n_seqs * heads * n * p
+            # 32-bit by the design: the decay's multiply, the two dot products with key and query and the write's multiply-add per
+            # state element and token on the fp32 pipe, against the nominal fp32 rate: 128 lanes x 2 x 1.965 GHz per SM
+            import torch as _t
+
+            fp32_rate = _t.cuda.get_device_properties(0).multi_processor_count * 128 * 2 * 1.965e9
+            ideal = max(7.0 * rows * heads * n * p / fp32_rate, byts / (self.peaks["hbm_gbs"] * 1e9)) * 1e6
+            return ideal, 7.0 * rows * heads * n * p, byts
+        elif name == "min_gru":
+            out, n_seqs = args[0], args[8]
+            byts = out.numel() * (12 + out.element_size()) + 8 * n_seqs * out.shape[1]
+        elif name == "hyper_connect":
+            # the streams read once, and written once when a sublayer's output is owed; that output, the next input and the sum once each
+            streams = args[0]
+            given = lambda i, key: (args[i] if len(args) > i else kwargs.get(key))
+            y, x_out, sum_out = given(1, "y"), given(7, "x_out"), given(8, "sum_out")
+            byts = streams.numel() * 4 * (2 if y is not None else 1) + sum(t.numel() * t.element_size() for t in (y, x_out, sum_out) if t is not None)
         elif name == "causal_conv":
             out = args[0]
             byts = 8 * out.numel() + 8 * args[9] * (args[3].shape[1] - 1) * out.shape[1]
@@ -615,7 +684,7 @@ class DesignBench(Bench):
     """One engine of one design at one size, measured like the headline bench's."""
 
     def __init__(self, architecture: str, cfg, label: str, vocab: int, weight_bytes: int, kv_bytes_per_token: int, flops_per_token: float, attn_flops_per_pair: float, max_batch: int,
-                 state_bytes_per_request: int = 0):
+                 state_bytes_per_request: int = 0, window: int = 0):
         import numpy as np
 
         from alofa_b200.engine.engine import Engine
@@ -627,11 +696,18 @@ class DesignBench(Bench):
         self.runner = self.engine.runner
         self.numbers = {"weight_bytes": weight_bytes, "kv_bytes_per_token": kv_bytes_per_token, "state_bytes_per_request": state_bytes_per_request}
         self.flops_per_token, self.attn_flops_per_pair = flops_per_token, attn_flops_per_pair
+        self.window = window  # every attention of the design sees this many keys at most (0: all)
         self.peaks, self.peaks_kind = peaks()
         self.rng = np.random.default_rng(0)
 
     def prompt(self, n: int) -> list:
         return [int(t) for t in self.rng.integers(0, self.vocab, size=n)]
+
+    def pairs(self, tokens: int) -> float:
+        """(query, visible key) pairs of one prompt of ``tokens`` tokens."""
+        if not self.window or self.window >= tokens:
+            return tokens * (tokens + 1) / 2
+        return self.window * (self.window + 1) / 2 + (tokens - self.window) * self.window
 
     def prefill(self, warmup: int, reps: int = 10) -> dict:
         from alofa_b200.engine.step import StepEntry
@@ -647,7 +723,7 @@ class DesignBench(Bench):
             one()
         _, each = self.timed_each(one, reps)
         ms = statistics.median(each)
-        flops = self.flops_per_token * PROMPT_LEN + self.attn_flops_per_pair * PROMPT_LEN * (PROMPT_LEN + 1) / 2
+        flops = self.flops_per_token * PROMPT_LEN + self.attn_flops_per_pair * self.pairs(PROMPT_LEN)
         return {"tok_s": round(PROMPT_LEN / ms * 1e3, 1), "ms": round(ms, 4), "flops_frac": round(flops / (ms * 1e-3) / (self.peaks["bf16_tflops"] * 1e12), 4)}
 
     def kernels(self, batch: int) -> dict:
@@ -663,14 +739,15 @@ class DesignBench(Bench):
             runner.forward_logits([StepEntry(slot, tokens, (PROMPT_LEN - 1,))])  # loads every kernel
             runner.release(slot)
             slot = runner.admit(30_001)
-            prefill = clock.run(lambda: runner.forward_logits([StepEntry(slot, tokens, (PROMPT_LEN - 1,))]), PROMPT_LEN, PROMPT_LEN * (PROMPT_LEN + 1) / 2)
+            prefill = clock.run(lambda: runner.forward_logits([StepEntry(slot, tokens, (PROMPT_LEN - 1,))]), PROMPT_LEN, self.pairs(PROMPT_LEN))
             runner.release(slot)
             slots = [runner.admit(31_000 + i) for i in range(batch)]
             for s_ in slots:
                 runner.forward_logits([StepEntry(s_, self.prompt(PROMPT_LEN), ())])
             one = lambda: runner.forward_logits([StepEntry(s_, (1,), (0,)) for s_ in slots])
             one()
-            decode = clock.run(one, batch * (PROMPT_LEN + 2), batch * (PROMPT_LEN + 2))
+            seen = min(PROMPT_LEN + 2, self.window or PROMPT_LEN + 2)
+            decode = clock.run(one, batch * seen, batch * seen)
             for s_ in slots:
                 runner.release(s_)
         finally:
@@ -720,23 +797,34 @@ def darolix_numbers(z: dict, d: dict) -> dict:
 
 def run_designs(args) -> dict:
     """Prefill and decode of a design beside its closest existing design at equal layer sizes (Kotutar
-    beside Qwen2, Darolix beside Kotutar), and the kernels of one step of each against their own rooflines."""
-    from alofa_b200.models import darolix, kotutar, qwen2
+    beside Qwen2, Darolix beside Kotutar, Dibulix beside Darolix), and the kernels of one step of each
+    against their own rooflines."""
+    from alofa_b200.models import darolix, dibulix, kotutar, qwen2
 
-    pair = "Darolix design beside Kotutar" if args.design == "darolix" else "Kotutar design beside Qwen2"
+    pair = {"dibulix": "Dibulix design beside Darolix", "darolix": "Darolix design beside Kotutar", "kotutar": "Kotutar design beside Qwen2"}[args.design]
     out = {"metric": f"prefill and decode of the {pair} at equal layer sizes", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
            "prompt_tokens": PROMPT_LEN, "context": CONTEXT, "steps": args.steps, "warmup": args.warmup, "sizes": {}}
     for size in ([args.size] if args.size else sorted(DESIGN_SIZES)):
         z = DESIGN_SIZES[size]
         row = {"sizes": z}
-        if args.design == "darolix":
+        if args.design == "dibulix":
+            row["dibulix_sizes"], row["darolix_sizes"] = DIBULIX_SIZES[size], DAROLIX_SIZES[size]
+            arms = (("dibulix", dibulix.NAME, dibulix_config(z, DIBULIX_SIZES[size])), ("darolix", darolix.NAME, darolix_config(z, DAROLIX_SIZES[size])))
+        elif args.design == "darolix":
             row["darolix_sizes"] = DAROLIX_SIZES[size]
             arms = (("darolix", darolix.NAME, darolix_config(z, DAROLIX_SIZES[size])), ("kotutar", kotutar.NAME, kotutar_config_routed(z)))
         else:
             arms = (("kotutar", kotutar.NAME, kotutar_config(z)), ("qwen2", qwen2.NAME, qwen2_config_like(z)))
         for design, name, cfg in arms:
-            n = darolix_numbers(z, DAROLIX_SIZES[size]) if design == "darolix" else design_numbers(design, z, routed_only=args.design == "darolix")
-            bench = DesignBench(name, cfg, f"{design} {size}", z["vocab"], n["weight_bytes"], n["kv_bytes_per_token"], n["flops_per_token"], n["attn_flops_per_pair"], 64, n.get("state_bytes_per_request", 0))
+            if design == "dibulix":
+                n = dibulix_numbers(z, DIBULIX_SIZES[size])
+            elif design == "darolix":
+                n = darolix_numbers(z, DAROLIX_SIZES[size])
+            else:
+                n = design_numbers(design, z, routed_only=args.design == "darolix")
+            window = DIBULIX_SIZES[size]["window"] if design == "dibulix" else 0
+            bench = DesignBench(name, cfg, f"{design} {size}", z["vocab"], n["weight_bytes"], n["kv_bytes_per_token"], n["flops_per_token"], n["attn_flops_per_pair"], 64,
+                                n.get("state_bytes_per_request", 0), window=window)
             res = {"prefill_2048": bench.prefill(args.warmup)}
             for batch in (8, 64):
                 point = bench.decode(batch, min(args.steps, 64), args.warmup)
@@ -766,7 +854,7 @@ def main() -> int:
     ap.add_argument("--phase", choices=["all", "decode", "prefill"], default="all", help="profiling aid: run only one part; the JSON line then lacks the others")
     ap.add_argument("--shape", choices=sorted(SHAPES), default="0.5b", help="whose layer sizes the headline run has")
     ap.add_argument("--no-extra", dest="extra", action="store_false", help="leave out the measurements beside the headline (long contexts, the 1.5B and 7B shapes)")
-    ap.add_argument("--design", choices=["kotutar", "darolix"], help="instead of the headline run: this design beside its closest existing one (Qwen2 for kotutar, Kotutar for darolix) at equal layer sizes (prefill, decode, kernels against their rooflines)")
+    ap.add_argument("--design", choices=["kotutar", "darolix", "dibulix"], help="instead of the headline run: this design beside its closest existing one (Qwen2 for kotutar, Kotutar for darolix, Darolix for dibulix) at equal layer sizes (prefill, decode, kernels against their rooflines)")
     ap.add_argument("--size", choices=sorted(DESIGN_SIZES), help="with --design: one of the sizes only")
     args = ap.parse_args()
     if args.impl == "reference":
