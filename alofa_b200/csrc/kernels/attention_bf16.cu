@@ -45,7 +45,14 @@ struct AttnParams {
   float cap_in, cap_out;  // scale / softcap and softcap / scale: scores are cap_out * tanh(dot * cap_in) before the scale
 #endif
   int* status;           // set to 2 when a wait on a bulk copy gave up (may be null)
+  const float* sink;     // [nh] or null: one more term exp(sink[h]) of the softmax's denominator, with no key and no value
 };
+
+// The sink's share of a row's sum whose terms are scaled by 2^-m_log2 (m_log2: the row's maximum in log2 units).
+// Added where a row's sum is complete: the kernel that merges key splits adds it when there are any.
+__device__ __forceinline__ float sink_term(const float* sink, int head, float m_log2) {
+  return sink ? exp2f(fmaf(sink[head], 1.4426950408889634f, -m_log2)) : 0.f;
+}
 
 #include "attention_prefill_tc.cuh"
 
@@ -319,7 +326,7 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
         ml[1] = l;
       }
     } else {
-      const float inv = 1.0f / l;
+      const float inv = 1.0f / (l + sink_term(p.sink, kvh * g + row % g, m * p.scale_log2));
       bf16* po = p.out + out_row * HD;
 #pragma unroll
       for (int d = 0; d < DTILES; ++d)
@@ -557,7 +564,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
     }
     const size_t out_row = (size_t)token * p.nh + kvh * g + r;
     if (single) {
-      p.out[out_row * HD + d] = __float2bfloat16_rn(acc / l);
+      p.out[out_row * HD + d] = __float2bfloat16_rn(acc / (l + sink_term(p.sink, kvh * g + r, m)));
     } else {
       p.partial_o[((size_t)split * p.n_rows_total + out_row) * HD + d] = acc;
       if (d == 0) {
@@ -602,7 +609,8 @@ static int launch_decode(const AttnParams& p, const CUtensorMap& map_k, const CU
 // Merge the splits of every (token, head) row in split order.  One block of HD
 // threads per row; a row's splits are those its visible keys fall into.
 __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
-                                         const int* __restrict__ positions, int nh, int window, int split_keys, int n_rows_total) {
+                                         const int* __restrict__ positions, int nh, int window, int split_keys, int n_rows_total,
+                                         const float* __restrict__ sink) {
   const int row = blockIdx.x;       // token * nh + head
   pdl_begin();
   const int P = positions[row / nh];
@@ -619,7 +627,7 @@ __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* __
     l += ml[1] * w;
     acc += partial_o[((size_t)s * n_rows_total + row) * HD + d] * w;
   }
-  out[(size_t)row * HD + d] = __float2bfloat16_rn(acc / l);
+  out[(size_t)row * HD + d] = __float2bfloat16_rn(acc / (l + sink_term(sink, row % nh, m)));
 }
 
 constexpr int PREFILL_STAGES = 2, SPLIT_STAGES = 4;
@@ -669,10 +677,10 @@ ALOFA_API int alofa_attention_decode_slots(int page_size, int warps) {
 
 // Merge the splits a launch with do_combine = 0 left behind: out [T, nh, HD] bf16.
 ALOFA_API int alofa_attention_combine(void* out, const float* partial_o, const float* partial_ml, const int* positions, int n_tokens, int nh,
-                                      int window, int split_keys, cudaStream_t stream) {
+                                      int window, int split_keys, const float* sink, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
   if (!partial_o || !partial_ml || !positions || split_keys <= 0) return ALOFA_ERR_ARGUMENT;
-  launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, n_tokens * nh);
+  launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, n_tokens * nh, sink);
   return launch_status();
 }
 
@@ -687,7 +695,8 @@ ALOFA_API int alofa_attention_combine(void* out, const float* partial_o, const f
 ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache, const int* q_start, const int* kv_len, const int* positions,
                                    const int* block_table, int max_blocks, int page_size, int n_seqs, int n_tokens, int tiles, int nh, int nkv,
                                    int window, float scale, int n_splits, int split_keys, float* partial_o, float* partial_ml,
-                                   int max_kv_len, long long cache_slots, int* status, int do_combine, float softcap, cudaStream_t stream) {
+                                   int max_kv_len, long long cache_slots, int* status, int do_combine, float softcap, const float* sink,
+                                   cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return ALOFA_OK;
 #ifdef SOFTCAP
   if (!(softcap > 0.f) || !(scale > 0.f)) return ALOFA_ERR_ARGUMENT;
@@ -698,7 +707,9 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
   if (n_splits > 0 && (split_keys <= 0 || split_keys % BLOCK_N != 0 || !partial_o || !partial_ml || !positions)) return ALOFA_ERR_ARGUMENT;
   const bool decode_only = n_seqs == n_tokens;
   if (n_splits > 0 && decode_only && nh / nkv > BLOCK_M) return ALOFA_ERR_ARGUMENT;
+  if (sink && n_splits > 1 && !do_combine) return ALOFA_ERR_ARGUMENT;  // the sink is added where the splits are merged: here
   AttnParams p;
+  p.sink = sink;
   p.out = (bf16*)out;
   p.q = (const bf16*)q;
   p.status = status;
@@ -765,17 +776,17 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
       rc = tma ? launch_decode<2, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream) : launch_decode<2, false>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);
     if (rc != ALOFA_OK) return rc;
     if (n_splits > 1 && do_combine)
-      launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, p.n_rows_total);
+      launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, p.n_rows_total, p.sink);
   } else if (n_splits > 0 && !decode_only) {
     // prompt portions: every query tile's keys split over n_splits CTAs, so that the tiles
     // at the end of a long prompt do not set the pace
     launch_dep(attention_bf16_kernel<true, PREFILL_STAGES>, dim3(tiles * n_splits, nkv, n_seqs), 128, smem, stream, p);
     if (cudaGetLastError() != cudaSuccess) return ALOFA_ERR_LAUNCH;
-    launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, p.n_rows_total);
+    launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, p.n_rows_total, p.sink);
   } else if (n_splits > 0) {
     launch_dep(attention_bf16_kernel<true, SPLIT_STAGES>, dim3(n_splits, nkv, n_seqs), 128, smem, stream, p);
     if (cudaGetLastError() != cudaSuccess) return ALOFA_ERR_LAUNCH;
-    launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, p.n_rows_total);
+    launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, p.n_rows_total, p.sink);
   } else {
     // prompt portions: the tcgen05 kernel where the head size and the pages are its own
     // (ALOFA_ATTENTION_TC=0 keeps the mma.sync kernel), else mma.sync

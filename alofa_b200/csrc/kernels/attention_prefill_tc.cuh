@@ -328,7 +328,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attention_prefill_tc_kernel(con
     l += row_max[0][half ^ 1][r];
     if (ok) {
       tc_fence_after();
-      const float inv = 1.0f / l;
+      const float inv = 1.0f / (l + sink_term(p.sink, kvh * g + (row_ok ? R % g : 0), m_used));
       bf16* dst = p.out + ((size_t)(row_begin + (row_ok ? R / g : 0)) * p.nh + kvh * g + (row_ok ? R % g : 0)) * HD + half * OCOLS;
 #pragma unroll
       for (int c0 = 0; c0 < OCOLS; c0 += 16) {

@@ -19,38 +19,91 @@ __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + lo
 
 // ---------------------------------------------------------------------------
 // min_gru: u [T, ld] fp32 holds the projections' sums (biases added) at columns z_off, x_off, g_off;
-// out [T, width] in the compute dtype; state [slots][>= width] fp32.  A thread per (request, channel).
+// out [T, width] in the compute dtype; state [slots][>= width] fp32.  A block takes 32 channels (a
+// lane each) of one request; its warps share the request's tokens of the step, a stretch of
+// consecutive tokens each.  The recurrence is linear in the state, so a stretch is the map
+// S -> A S + B with A = prod (1 - z_t) and B its result from a zero state: every warp finds its
+// stretch's (A, B), the stretches before it give its starting state (in order, from the request's
+// stored state), and it then walks its stretch and writes the outputs.  A warp reads GRU_AHEAD
+// tokens' inputs before it uses the first, so that the loads do not wait on one another.  Decode
+// steps are launched with one warp a block, which walks its (one) token from the stored state.
 // ---------------------------------------------------------------------------
+constexpr int GRU_AHEAD = 8;
+constexpr int GRU_MAX_WARPS = 16;
+
+__device__ __forceinline__ float gru_candidate(float x) { return x >= 0.f ? x + 0.5f : sigmoid_f(x); }
+
 template <typename TO>
-__global__ void __launch_bounds__(64) min_gru_kernel(TO* __restrict__ out, const float* __restrict__ u, int ld, int z_off, int x_off, int g_off,
-                                                     float* __restrict__ state, long long slot_stride, const int* __restrict__ q_start,
-                                                     const int* __restrict__ state_slots, int width) {
+__global__ void __launch_bounds__(GRU_MAX_WARPS * 32) min_gru_kernel(TO* __restrict__ out, const float* __restrict__ u, int ld, int z_off, int x_off, int g_off,
+                                                                      float* __restrict__ state, long long slot_stride, const int* __restrict__ q_start,
+                                                                      const int* __restrict__ state_slots, int width) {
+  __shared__ float seg_a[GRU_MAX_WARPS][32], seg_b[GRU_MAX_WARPS][32];
   pdl_begin();
-  const int c = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
-  if (c >= width) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int c = blockIdx.x * 32 + lane, s = blockIdx.y;
+  const bool live = c < width;
   const int t0 = q_start[s], t1 = q_start[s + 1];
-  if (t0 >= t1) return;
+  if (t0 >= t1) return;  // the whole block
+  const int per = (t1 - t0 + warps - 1) / warps;
+  const int a = min(t0 + warp * per, t1), b = min(a + per, t1);
+  const float* col = u + (live ? c : 0);
+  if (warps > 1) {
+    float A = 1.f, B = 0.f;
+    for (int t = a; t < b; t += GRU_AHEAD) {
+      float zs[GRU_AHEAD], xs[GRU_AHEAD];
+#pragma unroll
+      for (int i = 0; i < GRU_AHEAD; ++i) {
+        const float* row = col + (size_t)min(t + i, b - 1) * ld;
+        zs[i] = row[z_off];
+        xs[i] = row[x_off];
+      }
+#pragma unroll
+      for (int i = 0; i < GRU_AHEAD; ++i) {
+        if (t + i >= b) break;
+        const float z = sigmoid_f(zs[i]);
+        B = (1.0f - z) * B + z * gru_candidate(xs[i]);
+        A *= 1.0f - z;
+      }
+    }
+    seg_a[warp][lane] = A;
+    seg_b[warp][lane] = B;
+    __syncthreads();
+  }
+  if (a >= b || !live) return;
   float* st = state + (long long)state_slots[s] * slot_stride + c;
   float S = *st;
-  for (int t = t0; t < t1; ++t) {
-    const float* row = u + (size_t)t * ld + c;
-    const float z = sigmoid_f(row[z_off]);
-    const float x = row[x_off];
-    const float cand = x >= 0.f ? x + 0.5f : sigmoid_f(x);
-    S = (1.0f - z) * S + z * cand;
-    const float g = row[g_off];
-    out[(size_t)t * width + c] = from_f<TO>(S * (g / (1.0f + expf(-g))));
+  for (int w = 0; w < warp; ++w) S = seg_a[w][lane] * S + seg_b[w][lane];
+  for (int t = a; t < b; t += GRU_AHEAD) {
+    float zs[GRU_AHEAD], xs[GRU_AHEAD], gs[GRU_AHEAD];
+#pragma unroll
+    for (int i = 0; i < GRU_AHEAD; ++i) {
+      const float* row = col + (size_t)min(t + i, b - 1) * ld;
+      zs[i] = row[z_off];
+      xs[i] = row[x_off];
+      gs[i] = row[g_off];
+    }
+#pragma unroll
+    for (int i = 0; i < GRU_AHEAD; ++i) {
+      if (t + i >= b) break;
+      const float z = sigmoid_f(zs[i]);
+      S = (1.0f - z) * S + z * gru_candidate(xs[i]);
+      out[(size_t)(t + i) * width + c] = from_f<TO>(S * (gs[i] / (1.0f + expf(-gs[i]))));
+    }
   }
-  *st = S;
+  if (b == t1) *st = S;  // the stretch that ends the request's tokens leaves the state
 }
 
+// n_tokens: rows of the step.  With as many rows as requests every request has one token.
 ALOFA_API int alofa_min_gru(void* out, const float* u, int ld, int z_off, int x_off, int g_off, float* state, long long slot_stride, const int* q_start,
-                            const int* state_slots, int n_seqs, int width, int out_bf16, cudaStream_t stream) {
+                            const int* state_slots, int n_seqs, int n_tokens, int width, int out_bf16, cudaStream_t stream) {
   if (n_seqs <= 0) return ALOFA_OK;
   if (width <= 0) return ALOFA_ERR_ARGUMENT;
-  const dim3 grid((width + 63) / 64, n_seqs);
-  if (out_bf16) launch_dep(min_gru_kernel<bf16>, grid, 64, 0, stream, (bf16*)out, u, ld, z_off, x_off, g_off, state, slot_stride, q_start, state_slots, width);
-  else launch_dep(min_gru_kernel<float>, grid, 64, 0, stream, (float*)out, u, ld, z_off, x_off, g_off, state, slot_stride, q_start, state_slots, width);
+  const dim3 grid((width + 31) / 32, n_seqs);
+  // stretches of 16 tokens or more: shorter ones cost more in the (A, B) pass than they save
+  int warps = 1;
+  while (warps < GRU_MAX_WARPS && (long long)n_tokens >= (long long)n_seqs * warps * 2 * 16) warps *= 2;
+  if (out_bf16) launch_dep(min_gru_kernel<bf16>, grid, warps * 32, 0, stream, (bf16*)out, u, ld, z_off, x_off, g_off, state, slot_stride, q_start, state_slots, width);
+  else launch_dep(min_gru_kernel<float>, grid, warps * 32, 0, stream, (float*)out, u, ld, z_off, x_off, g_off, state, slot_stride, q_start, state_slots, width);
   return launch_status();
 }
 

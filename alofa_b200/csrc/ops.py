@@ -97,9 +97,9 @@ def _attention(head_dim: int, capped: bool = False):
             defines["SOFTCAP"] = 1
         lib = load_library(f"alofa_{key}", ["kernels/attention_bf16.cu"], defines=defines)
         lib.alofa_attention_bf16.restype = _I
-        lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, ctypes.c_longlong, _P, _I, _F, _P]
+        lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, ctypes.c_longlong, _P, _I, _F, _P, _P]
         lib.alofa_attention_combine.restype = _I
-        lib.alofa_attention_combine.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _P]
+        lib.alofa_attention_combine.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P]
         lib.alofa_attention_decode_wide_warps.restype = _I
         lib.alofa_attention_decode_wide_warps.argtypes = []
         lib.alofa_attention_decode_slots.restype = _I
@@ -455,14 +455,15 @@ def gemm_tc_rope(x, w, bias, q_out, k_cache, v_cache, slot_map, positions, cos_s
 
 
 def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, positions, block_table, page_size, n_seqs, max_q_len, nh, nkv, hd, window, scale,
-                   n_splits: int = 0, split_keys: int = 0, partial_o=None, partial_ml=None, max_kv_len: int = 0, status=None, combine: bool = True, softcap: float = 0.0) -> None:
+                   n_splits: int = 0, split_keys: int = 0, partial_o=None, partial_ml=None, max_kv_len: int = 0, status=None, combine: bool = True, softcap: float = 0.0, sink=None) -> None:
     """Causal GQA over the paged bf16 cache for a step's requests; with
     ``n_splits`` > 0 the keys of each request (decode tokens) or of each query
     tile (prompt portions) are split over several CTAs and merged - unless
     ``combine`` is False (decode tokens only): then ``partial_o`` / ``partial_ml``
     keep the splits for :func:`attention_combine` or a product that merges them.
     ``softcap`` > 0 (the library built for it): scaled scores are bounded by
-    ``softcap * tanh(score / softcap)``."""
+    ``softcap * tanh(score / softcap)``.  ``sink`` [nh] fp32: one more term
+    ``exp(sink[h])`` of every row's denominator (merged splits only)."""
     n = q.shape[0]
     bf = torch.bfloat16
     g = nh // nkv
@@ -475,18 +476,20 @@ def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, positions, block_t
         _dev(partial_o, "partial_o", torch.float32) if partial_o is not None else None,
         _dev(partial_ml, "partial_ml", torch.float32) if partial_ml is not None else None,
         int(max_kv_len) if max_kv_len else block_table.shape[1] * page_size, k_cache.shape[0],
-        _dev(status, "status", torch.int32) if status is not None else None, 1 if combine else 0, float(softcap or 0.0), _stream(),
+        _dev(status, "status", torch.int32) if status is not None else None, 1 if combine else 0, float(softcap or 0.0),
+        _dev(sink, "sink", torch.float32) if sink is not None else None, _stream(),
     )
     _done(rc, "attention_bf16", f"hd={hd} nh={nh} nkv={nkv} splits={n_splits}")
     if n_splits > 1 and combine:
         count_launches(1)
 
 
-def attention_combine(out, partial_o, partial_ml, positions, nh: int, hd: int, window, split_keys: int) -> None:
+def attention_combine(out, partial_o, partial_ml, positions, nh: int, hd: int, window, split_keys: int, sink=None) -> None:
     """Merge the key splits of decode tokens: out [T, nh * hd] bf16."""
     rc = _attention(hd).alofa_attention_combine(
         _dev(out, "out", torch.bfloat16), _dev(partial_o, "partial_o", torch.float32), _dev(partial_ml, "partial_ml", torch.float32),
-        _dev(positions, "positions", torch.int32), out.shape[0], nh, int(window or 0), split_keys, _stream(),
+        _dev(positions, "positions", torch.int32), out.shape[0], nh, int(window or 0), split_keys,
+        _dev(sink, "sink", torch.float32) if sink is not None else None, _stream(),
     )
     _done(rc, "attention_combine")
 
@@ -1131,7 +1134,7 @@ def _delta():
     if lib is None:
         lib = load_library("alofa_delta", ["kernels/delta.cu"])
         sigs = {
-            "alofa_min_gru": [_P, _P, _I, _I, _I, _I, _P, _L, _P, _P, _I, _I, _I, _P],
+            "alofa_min_gru": [_P, _P, _I, _I, _I, _I, _P, _L, _P, _P, _I, _I, _I, _I, _P],
             "alofa_delta_prepare": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _F, _P],
             "alofa_delta_scan": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         }
@@ -1161,7 +1164,7 @@ def min_gru(out, u, z_off: int, x_off: int, g_off: int, state, q_start, state_sl
         raise AlofaError("invalid_argument", "min_gru sizes disagree", f"out={tuple(out.shape)} u={tuple(u.shape)}")
     _slot_state(state, width, "min_gru")
     _done(_delta().alofa_min_gru(_dev(out, "out"), _dev(u, "u", torch.float32), u.shape[1], z_off, x_off, g_off, state.data_ptr(), state.stride(0),
-                                 _dev(q_start, "q_start", i32), _dev(state_slots, "state_slots", i32), n_seqs, width, _is_bf16(out, "out"), _stream()), "min_gru")
+                                 _dev(q_start, "q_start", i32), _dev(state_slots, "state_slots", i32), n_seqs, n, width, _is_bf16(out, "out"), _stream()), "min_gru")
 
 
 def delta_prepare(qn, kn, kq, g, beta, conv, dz, u, b_off: int, dt_bias, a_log, heads: int, groups: int, n: int, unit_eps: float, q_scale: float) -> None:

@@ -28,9 +28,12 @@ class PagedAttend:
     """Attention of a step's rows over a paged key/value cache, shared by the
     mixers that keep one: which kernel runs, and how a decode step's keys are
     split over CTAs.  The mixer gives ``nh``, ``nkv``, ``hd`` (keys and values
-    alike), ``q_dim``, ``window``, ``scale`` and ``softcap`` (0: none)."""
+    alike), ``q_dim``, ``window``, ``scale``, ``softcap`` (0: none) and ``sink``
+    (None, or a score per head that the softmax's denominator holds beside the
+    keys': the kernel that completes a row's sum adds it)."""
 
     softcap = 0.0
+    sink = None
 
     # Keys per CTA, at least, when a decode-only step splits each request's keys: four 64-key
     # blocks, one per warp.  Splits grow in steps of this (a warp then takes several blocks in
@@ -109,17 +112,18 @@ class PagedAttend:
             if splits:
                 po = ctx.buf((splits, ctx.n_tokens * self.nh, self.hd), torch.float32)
                 pml = ctx.buf((splits, ctx.n_tokens * self.nh, 2), torch.float32)
-            unmerged = ctx.decode_only and 1 < splits <= self.MERGE_IN_PRODUCT_SPLITS and self.nh // self.nkv <= 16 and ctx.n_tokens <= 16
+            unmerged = ctx.decode_only and 1 < splits <= self.MERGE_IN_PRODUCT_SPLITS and self.nh // self.nkv <= 16 and ctx.n_tokens <= 16 and self.sink is None
             ops.attention_bf16(
                 out, q, cache.k, cache.v, ctx.q_start, ctx.kv_len, ctx.positions, group.block_table, group.page_size, ctx.n_seqs, ctx.max_q_len,
                 self.nh, self.nkv, self.hd, self.window, self.scale, splits, per_split, po, pml, longest, ctx.status, combine=not unmerged, softcap=self.softcap,
+                sink=self.sink,
             )
             if unmerged:
                 return MergedSplits(po, pml, ctx.positions, ctx.n_tokens, self.nh, self.hd, self.window, per_split, ctx.buf)
             return out
         ops.paged_attention_generic(
             out, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size,
-            self.nh, self.nkv, self.hd, self.window, self.scale, self.softcap,
+            self.nh, self.nkv, self.hd, self.window, self.scale, self.softcap, None, self.sink,
         )
         return out
 

@@ -98,7 +98,7 @@ class NormedAttention(PagedAttend, Part):
         q = ctx.buf((n, self.q_dim), dt)
         ops.qkv_prepare(q, cache.k, cache.v, sums, ctx.positions, group.slot_map, self.heads, self.kv_heads, self.dim, self.vdim, self.qk_norm, self.eps, self.coef, self.every,
                         self.position.frequencies() if self.rot_dims else None, self.rot_dims)
-        if self.dim == self.vdim and self.sink is None:
+        if self.dim == self.vdim:
             out = self.attend(ctx, q, cache, group)  # the tensor-core kernels in bfloat16 for the head sizes they are built for, else the every-size kernel
         else:
             out = ctx.buf((n, self.heads * self.vdim), dt)

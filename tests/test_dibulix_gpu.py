@@ -292,6 +292,53 @@ def test_windowed_attention_with_a_sink_over_paged_keys(dtype, H, G, d, dv, dims
     assert_close(got, plain.attend(q, k, v, scale, window, sink=False).reshape(n, H * dv), KERNEL_TOL[dtype], "no sink")
 
 
+@pytest.mark.parametrize("H,G,d,dims,window,page", [(4, 2, 64, 32, 100, 64), (4, 1, 128, 64, 300, 64), (8, 2, 128, 128, 4096, 64), (3, 3, 32, 8, 70, 16), (6, 2, 64, 64, 257, 16)])
+def test_tensor_core_attention_with_a_sink(H, G, d, dims, window, page):
+    """The bfloat16 kernels for keys and values of one size (whole prompts, prompt portions, single tokens with their
+    keys in one split and in several that a second kernel merges): one added to the denominator against plain, other
+    sink scores against the every-size kernel."""
+    from alofa_b200.csrc import ops
+
+    rng = np.random.default_rng(12)
+    lengths = [1, 2, 63, 64, 65, 300, 700, window + 1 if window < 1000 else 129]
+    scale = d ** -0.5
+    plains, queries, k_cache, v_cache, table = windowed_case(rng, lengths, H, G, d, d, dims, 1e4, BF16, page)
+    want = [plain.attend(q, k, v, scale, window, sink=True).reshape(len(q), H * d) for q, k, v in plains]
+    kv_len = dev(np.array(lengths, dtype=np.int32))
+
+    def run(picks, sink, split_keys=0):
+        q = torch.cat([queries[r][picks[r]] for r in range(len(picks))]).contiguous()
+        counts = [len(p) for p in picks]
+        positions = dev(np.concatenate([np.array(p, dtype=np.int32) for p in picks]))
+        q_start = dev(np.concatenate([[0], np.cumsum(counts)]).astype(np.int32))
+        out = torch.empty_like(q)
+        splits, po, pml = 0, None, None
+        if split_keys:
+            splits = -(-max(lengths) // split_keys)
+            po = torch.empty(splits, q.shape[0] * H, d, device="cuda")
+            pml = torch.empty(splits, q.shape[0] * H, 2, device="cuda")
+        ops.attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, positions, table, page, len(picks), max(counts), H, G, d, window, scale, splits, split_keys, po, pml,
+                           max(lengths), sink=sink)
+        return out.float().cpu().numpy()
+
+    zero = torch.zeros(H, dtype=F32, device="cuda")
+    other = dev(np.linspace(-3.0, 4.0, H).astype(np.float32))
+    shapes = {"whole": ([list(range(n)) for n in lengths], 0), "portion": ([list(range(n // 2, n)) for n in lengths], 0), "last": ([[n - 1] for n in lengths], 0),
+              "last in splits": ([[n - 1] for n in lengths], 256)}
+    for what, (picks, split_keys) in shapes.items():
+        got, at = run(picks, zero, split_keys), 0
+        for r, p in enumerate(picks):
+            assert_close(got[at : at + len(p)], want[r][p], KERNEL_TOL[BF16], f"{what}: request {r} ({lengths[r]} keys)")
+            at += len(p)
+        q = torch.cat([queries[r][picks[r]] for r in range(len(picks))]).contiguous()
+        positions = dev(np.concatenate([np.array(p, dtype=np.int32) for p in picks]))
+        seq = dev(np.concatenate([np.full(len(p), r, dtype=np.int32) for r, p in enumerate(picks)]))
+        ref = torch.empty_like(q)
+        ops.paged_attention_generic(ref, q, k_cache, v_cache, positions, seq, table, page, H, G, d, window, scale, 0.0, d, other)
+        assert_close(run(picks, other, split_keys), ref.float().cpu().numpy(), KERNEL_TOL[BF16], f"{what}: other sink scores")
+        assert np.abs(run(picks, other, split_keys) - got).max() > 0.02, "the sink's score does not show"
+
+
 @pytest.mark.parametrize("dtype", [F32, BF16])
 @pytest.mark.parametrize("window", [3, 16, 17, 130, 600])
 def test_a_key_just_inside_and_just_outside_the_window(dtype, window):
