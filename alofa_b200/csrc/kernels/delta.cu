@@ -164,7 +164,9 @@ ALOFA_API int alofa_delta_prepare(float* qn, float* kn, float* kq, float* g, flo
 // ---------------------------------------------------------------------------
 // delta_scan: a block takes one (head, request) and PC value channels and walks the request's
 // tokens of the step in order.  The NS threads that share a value channel (neighbours in a warp)
-// each hold R key channels of its column in registers: channels ns, ns + NS, ...  The state lies
+// each hold R key channels of its column in registers, four neighbours at a time: channels 4 ns ..
+// 4 ns + 3, then those 4 NS further on, ... (a token's keys, queries and decays are then R / 4 loads of
+// 16 bytes each, and the NS threads' loads lie side by side in shared memory).  The state lies
 // in memory as [head][value channel][key channel].  Keys, queries, decays, values, beta and k . q
 // of TC tokens at a time come into shared memory by asynchronous copies, the next ones while
 // these are worked on.
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(const DeltaArgs a) {
   float st[R];
 #pragma unroll
   for (int j = 0; j < R; ++j) {
-    const int n = j * NS + ns;
+    const int n = (j >> 2) * 4 * NS + 4 * ns + (j & 3);
     st[j] = (live_p && n < N) ? S[n] : 0.f;
   }
   __syncthreads();
@@ -269,22 +271,25 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(const DeltaArgs a) {
     const float* vs = gs + TC * NW;
     const float* bs = vs + TC * PC;
     for (int tt = 0; tt < live; ++tt) {
-      const float* kr = ks + tt * NW + ns;
-      const float* qr = qs + tt * NW + ns;
-      const float* gr = gs + tt * NW + ns;
+      const float4* kr = reinterpret_cast<const float4*>(ks + tt * NW) + ns;
+      const float4* qr = reinterpret_cast<const float4*>(qs + tt * NW) + ns;
+      const float4* gr = reinterpret_cast<const float4*>(gs + tt * NW) + ns;
       float kk[R];
       float r0 = 0.f, r1 = 0.f, w0 = 0.f, w1 = 0.f;
 #pragma unroll
-      for (int j = 0; j < R; ++j) {
-        kk[j] = kr[j * NS];
-        st[j] *= gr[j * NS];
-        if (j & 1) {
-          r1 = fmaf(st[j], kk[j], r1);
-          w1 = fmaf(st[j], qr[j * NS], w1);
-        } else {
-          r0 = fmaf(st[j], kk[j], r0);
-          w0 = fmaf(st[j], qr[j * NS], w0);
-        }
+      for (int j4 = 0; j4 < R / 4; ++j4) {
+        const float4 k4 = kr[j4 * NS], q4 = qr[j4 * NS], g4 = gr[j4 * NS];
+        const int j = 4 * j4;
+        kk[j] = k4.x, kk[j + 1] = k4.y, kk[j + 2] = k4.z, kk[j + 3] = k4.w;
+        st[j] *= g4.x, st[j + 1] *= g4.y, st[j + 2] *= g4.z, st[j + 3] *= g4.w;
+        r0 = fmaf(st[j], k4.x, r0);
+        w0 = fmaf(st[j], q4.x, w0);
+        r1 = fmaf(st[j + 1], k4.y, r1);
+        w1 = fmaf(st[j + 1], q4.y, w1);
+        r0 = fmaf(st[j + 2], k4.z, r0);
+        w0 = fmaf(st[j + 2], q4.z, w0);
+        r1 = fmaf(st[j + 3], k4.w, r1);
+        w1 = fmaf(st[j + 3], q4.w, w1);
       }
       float r = r0 + r1, w = w0 + w1;
       for (int o = NS >> 1; o > 0; o >>= 1) {
@@ -301,7 +306,7 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(const DeltaArgs a) {
   if (live_p && t0 < t1) {
 #pragma unroll
     for (int j = 0; j < R; ++j) {
-      const int n = j * NS + ns;
+      const int n = (j >> 2) * 4 * NS + 4 * ns + (j & 3);
       if (n < N) S[n] = st[j];
     }
   }
