@@ -17,7 +17,8 @@ def all_libraries() -> list:
         {"name": "alofa_elementwise_bf16", "sources": ["kernels/elementwise_bf16.cu"]},
         # latent attention on tensor cores is built per latent size at first use; the size of the tests' model is built ahead
         {"name": "alofa_latent_attention_kv64_r32", "sources": ["kernels/latent_attention_bf16.cu"], "defines": {"KV_RANK": 64, "ROT": 32}},
-        *[{"name": f"alofa_attention_hd{hd}", "sources": ["kernels/attention_bf16.cu"], "defines": {"HEAD_DIM": hd}} for hd in (16, 32, 48, 64, 128)],
+        {"name": "alofa_latent_attention_kv96_r16", "sources": ["kernels/latent_attention_bf16.cu"], "defines": {"KV_RANK": 96, "ROT": 16}},
+        *[{"name": f"alofa_attention_hd{hd}", "sources": ["kernels/attention_bf16.cu"], "defines": {"HEAD_DIM": hd}} for hd in (16, 32, 48, 64, 80, 96, 128)],
         # the build whose scores are capped (softcap * tanh(score / softcap)), likewise per head size at first use; two sizes ahead
         *[{"name": f"alofa_attention_hd{hd}_cap", "sources": ["kernels/attention_bf16.cu"], "defines": {"HEAD_DIM": hd, "SOFTCAP": 1}} for hd in (64, 128)],
     ]

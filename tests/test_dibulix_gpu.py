@@ -317,7 +317,8 @@ def test_windowed_attention_with_a_sink_over_paged_keys(dtype, H, G, d, dv, dims
     assert_close(got, plain.attend(q, k, v, scale, window, sink=False).reshape(n, H * dv), KERNEL_TOL[dtype], "no sink")
 
 
-@pytest.mark.parametrize("H,G,d,dims,window,page", [(4, 2, 64, 32, 100, 64), (4, 1, 128, 64, 300, 64), (8, 2, 128, 128, 4096, 64), (3, 3, 32, 8, 70, 16), (6, 2, 64, 64, 257, 16)])
+@pytest.mark.parametrize("H,G,d,dims,window,page", [(4, 2, 64, 32, 100, 64), (4, 1, 128, 64, 300, 64), (8, 2, 128, 128, 4096, 64), (3, 3, 32, 8, 70, 16), (6, 2, 64, 64, 257, 16),
+                                                   (6, 2, 96, 40, 75, 64), (2, 2, 80, 80, 300, 16)])
 def test_tensor_core_attention_with_a_sink(H, G, d, dims, window, page):
     """The bfloat16 kernels for keys and values of one size (whole prompts, prompt portions, single tokens with their
     keys in one split and in several that a second kernel merges): one added to the denominator against plain, other
@@ -453,7 +454,7 @@ def test_latent_attention_with_halves_paired_scaled_frequencies_and_a_head_gate(
 # ---------------------------------------------------------------------------------------------------
 # whole models
 # ---------------------------------------------------------------------------------------------------
-LENGTHS = {"A": [1, 2, 23, 64, 65, 129, 200], "B": [3, 16, 17, 33, 80, 131], "C": [5, 64, 190, 257], "D": [2, 63, 150, 300]}
+LENGTHS = {"A": [1, 2, 23, 64, 65, 129, 200], "B": [3, 16, 17, 33, 80, 131], "C": [5, 64, 190, 257], "D": [2, 63, 150, 300], "E": [4, 76, 140, 330]}
 DECODED = 12
 
 

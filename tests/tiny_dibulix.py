@@ -67,6 +67,13 @@ CONFIGS = {
                      layer("latent_attention", latent(2, 8, 16, 16, 32, 0.2, rot(1000.0, 16, (16.0, 256, 16.0, 2.0)), 130), None),
                      layer("channel_delta", delta(1, 1, 130, 8, 2), 32),
                      layer("latent_attention", latent(2, 16, 16, 8, 48, 0.18, rot(1000.0, 16, (3.0, 32, 6.0, 1.0)), 33), 32)]},
+    # five streams; head sizes 96 and 80 with keys and values alike, which the bfloat16 attention kernels are built for at first use (neither
+    # 64 nor 128: no bulk copies), part of a head turned and all of it; a latent of 96 with three heads; windows of 50, 75 and 300; three taps
+    "E": {"architecture": "Dibulix", "vocab": 400, "width": 192, "norm": {"eps": 2e-6}, "logit_scale": 0.4, "streams": 5,
+          "layers": [layer("latent_attention", latent(3, 48, 16, 40, 96, 0.13, rot(40000.0, 16, (4.0, 128, 16.0, 2.0)), 50), None),
+                     layer("parallel", parallel(6, 2, 96, 96, 0.1, rot(20000.0, 40), 75, 200, 0.8, 1.1), 256),
+                     layer("channel_delta", delta(6, 2, 48, 80, 3), None),
+                     layer("parallel", parallel(2, 2, 80, 80, 0.11, rot(3000.0, 80), 300, 96, 1.2, 0.7), 128)]},
 }
 
 
