@@ -83,7 +83,7 @@ class CacheStorage:
             if isinstance(spec, PagedKV):
                 slots = g.num_pages * g.block_size
                 k = torch.zeros((slots, spec.num_kv_heads, spec.head_dim), dtype=dtype, device=device)
-                v = torch.zeros((slots, spec.num_kv_heads, spec.v_head_dim or spec.head_dim), dtype=dtype, device=device)
+                v = torch.zeros((slots, spec.v_heads or spec.num_kv_heads, spec.v_head_dim or spec.head_dim), dtype=dtype, device=device)
                 self.bytes += (k.numel() + v.numel()) * k.element_size()
                 return LayerCache(gi, k, v)
             rows = torch.zeros((g.num_pages * g.block_size, spec.width), dtype=dtype, device=device)
@@ -110,7 +110,7 @@ class CacheStorage:
         out = {}
         for spec in flat_specs(plan):
             if isinstance(spec, PagedKV):
-                out[spec.window] = out.get(spec.window, 0) + spec.num_kv_heads * (spec.head_dim + (spec.v_head_dim or spec.head_dim)) * width
+                out[spec.window] = out.get(spec.window, 0) + (spec.num_kv_heads * spec.head_dim + (spec.v_heads or spec.num_kv_heads) * (spec.v_head_dim or spec.head_dim)) * width
             elif isinstance(spec, PagedRows):
                 out[spec.window] = out.get(spec.window, 0) + spec.width * width
         return out

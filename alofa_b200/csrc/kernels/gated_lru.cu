@@ -1,0 +1,172 @@
+// The real-gated linear recurrent unit: a recurrence element by element whose decay and input gate
+// are made from the (convolved) input of the current token by block-diagonal maps,
+//
+//   r = sigmoid(A_b u_b + a_b),  i = sigmoid(I_b u_b + i_b)       per block b of the channels
+//   log a = -c * r * softplus(lam),  a = exp(log a)
+//   S_t = a * S_(t-1) + sqrt(1 - a^2) * i * u
+//
+// and whose output is S_t times the activated other branch.  Everything here is fp32 (the gates'
+// sums too: plain multiply-adds in a fixed order over the block's inputs), in prompts and decoding
+// alike, so that a position's value does not depend on how the prompt was cut or on what else is
+// in the batch.
+#include "common.cuh"
+
+__device__ __forceinline__ float lru_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// ---------------------------------------------------------------------------
+// lru_gates: u [T, W] fp32; wa, wi [B][bs][bs] fp32 stored [block][in][out] (the transposes of the
+// checkpoint's [out, in], so that the threads of a warp read neighbouring numbers); ba, bi [W];
+// rate [W] = -c * softplus(lam), made once at load.  Writes a [T, W] and the driven input
+// b = sqrt(1 - a^2) * i * u [T, W].  A block takes LRU_TT tokens, one block of the channels and
+// LRU_OT of its outputs, a thread per output; the tokens' inputs lie in shared memory.
+// ---------------------------------------------------------------------------
+constexpr int LRU_TT = 8;
+constexpr int LRU_OT = 128;
+
+__global__ void __launch_bounds__(LRU_OT) lru_gates_kernel(float* __restrict__ a_out, float* __restrict__ b_out, const float* __restrict__ u, const float* __restrict__ wa,
+                                                           const float* __restrict__ wi, const float* __restrict__ ba, const float* __restrict__ bi,
+                                                           const float* __restrict__ rate, int n_tokens, int W, int bs) {
+  extern __shared__ float lru_us[];  // [LRU_TT][bs]
+  pdl_begin();
+  const int t0 = blockIdx.x * LRU_TT, blk = blockIdx.y, o = blockIdx.z * LRU_OT + threadIdx.x;
+  const int live = min(LRU_TT, n_tokens - t0);
+  for (int e = threadIdx.x; e < LRU_TT * bs; e += LRU_OT) {
+    const int r = e / bs, c = e - r * bs;
+    lru_us[e] = r < live ? u[(size_t)(t0 + r) * W + blk * bs + c] : 0.f;
+  }
+  __syncthreads();
+  if (o >= bs) return;
+  float sa[LRU_TT], si[LRU_TT];
+#pragma unroll
+  for (int r = 0; r < LRU_TT; ++r) sa[r] = si[r] = 0.f;
+  const float* pa = wa + (size_t)blk * bs * bs + o;
+  const float* pi = wi + (size_t)blk * bs * bs + o;
+#pragma unroll 4
+  for (int k = 0; k < bs; ++k) {
+    const float va = pa[(size_t)k * bs], vi = pi[(size_t)k * bs];
+#pragma unroll
+    for (int r = 0; r < LRU_TT; ++r) {
+      const float x = lru_us[r * bs + k];
+      sa[r] = fmaf(va, x, sa[r]);
+      si[r] = fmaf(vi, x, si[r]);
+    }
+  }
+  const int ch = blk * bs + o;
+  const float bias_a = ba[ch], bias_i = bi[ch], rt = rate[ch];
+#pragma unroll
+  for (int r = 0; r < LRU_TT; ++r) {
+    if (r >= live) break;
+    const float gate_r = lru_sigmoid(sa[r] + bias_a), gate_i = lru_sigmoid(si[r] + bias_i);
+    const float log_a = rt * gate_r;  // never positive
+    const float a = expf(log_a);
+    const float keep = sqrtf(-expm1f(2.0f * log_a));  // sqrt(1 - a^2) without the cancellation near a = 1
+    const size_t at = (size_t)(t0 + r) * W + ch;
+    a_out[at] = a;
+    b_out[at] = keep * gate_i * lru_us[r * bs + o];
+  }
+}
+
+ALOFA_API int alofa_lru_gates(float* a_out, float* b_out, const float* u, const float* wa, const float* wi, const float* ba, const float* bi, const float* rate,
+                              int n_tokens, int W, int blocks, cudaStream_t stream) {
+  if (n_tokens <= 0) return ALOFA_OK;
+  if (W <= 0 || blocks <= 0 || W % blocks) return ALOFA_ERR_ARGUMENT;
+  const int bs = W / blocks;
+  const size_t smem = (size_t)LRU_TT * bs * sizeof(float);
+  if (smem > 200 * 1024) return ALOFA_ERR_ARGUMENT;
+  static size_t set = 48 * 1024;
+  if (smem > set) {
+    if (cudaFuncSetAttribute(lru_gates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
+    set = smem;
+  }
+  launch_dep(lru_gates_kernel, dim3((n_tokens + LRU_TT - 1) / LRU_TT, blocks, (bs + LRU_OT - 1) / LRU_OT), LRU_OT, smem, stream, a_out, b_out, u, wa, wi, ba, bi, rate,
+             n_tokens, W, bs);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// lru_scan: S_t = a_t S_(t-1) + b_t over each request's tokens of the step in order, out[t] = S_t *
+// act(y[t]) with y the other branch's fp32 sums at column y_off of rows of ldy numbers (act: a code
+// of the activations in common.cuh).  A block takes 32 channels (a lane each) of one request; its
+// warps share the request's tokens of the step, a stretch of consecutive tokens each.  The
+// recurrence is linear in the state, so a stretch is the map S -> A S + B with A the product of its
+// decays and B its result from a zero state: every warp finds its stretch's (A, B), the stretches
+// before it give its starting state (in order, from the request's stored state), and it then walks
+// its stretch and writes the outputs.  A warp reads LRU_AHEAD tokens' inputs before it uses the
+// first, so that the loads do not wait on one another.  Decode steps are launched with one warp a
+// block, which walks its (one) token from the stored state.
+// ---------------------------------------------------------------------------
+constexpr int LRU_AHEAD = 8;
+constexpr int LRU_MAX_WARPS = 16;
+
+template <typename TO>
+__global__ void __launch_bounds__(LRU_MAX_WARPS * 32) lru_scan_kernel(TO* __restrict__ out, const float* __restrict__ a_in, const float* __restrict__ b_in,
+                                                                       const float* __restrict__ y, int ldy, int y_off, int act, float* __restrict__ state,
+                                                                       long long slot_stride, const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                                                                       int width) {
+  __shared__ float seg_a[LRU_MAX_WARPS][32], seg_b[LRU_MAX_WARPS][32];
+  pdl_begin();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int c = blockIdx.x * 32 + lane, s = blockIdx.y;
+  const bool live = c < width;
+  const int t0 = q_start[s], t1 = q_start[s + 1];
+  if (t0 >= t1) return;  // the whole block
+  const int per = (t1 - t0 + warps - 1) / warps;
+  const int lo = min(t0 + warp * per, t1), hi = min(lo + per, t1);
+  const int cc = live ? c : 0;
+  if (warps > 1) {
+    float A = 1.f, B = 0.f;
+    for (int t = lo; t < hi; t += LRU_AHEAD) {
+      float as[LRU_AHEAD], bs[LRU_AHEAD];
+#pragma unroll
+      for (int i = 0; i < LRU_AHEAD; ++i) {
+        const size_t at = (size_t)min(t + i, hi - 1) * width + cc;
+        as[i] = a_in[at];
+        bs[i] = b_in[at];
+      }
+#pragma unroll
+      for (int i = 0; i < LRU_AHEAD; ++i) {
+        if (t + i >= hi) break;
+        B = fmaf(as[i], B, bs[i]);
+        A *= as[i];
+      }
+    }
+    seg_a[warp][lane] = A;
+    seg_b[warp][lane] = B;
+    __syncthreads();
+  }
+  if (lo >= hi || !live) return;
+  float* st = state + (long long)state_slots[s] * slot_stride + c;
+  float S = *st;
+  for (int w = 0; w < warp; ++w) S = fmaf(seg_a[w][lane], S, seg_b[w][lane]);
+  for (int t = lo; t < hi; t += LRU_AHEAD) {
+    float as[LRU_AHEAD], bs[LRU_AHEAD], ys[LRU_AHEAD];
+#pragma unroll
+    for (int i = 0; i < LRU_AHEAD; ++i) {
+      const size_t row = (size_t)min(t + i, hi - 1);
+      as[i] = a_in[row * width + c];
+      bs[i] = b_in[row * width + c];
+      ys[i] = y[row * ldy + y_off + c];
+    }
+#pragma unroll
+    for (int i = 0; i < LRU_AHEAD; ++i) {
+      if (t + i >= hi) break;
+      S = fmaf(as[i], S, bs[i]);
+      out[(size_t)(t + i) * width + c] = from_f<TO>(S * activate(ys[i], act));
+    }
+  }
+  if (hi == t1) *st = S;  // the stretch that ends the request's tokens leaves the state
+}
+
+// n_tokens: rows of the step.  With as many rows as requests every request has one token.
+ALOFA_API int alofa_lru_scan(void* out, const float* a, const float* b, const float* y, int ldy, int y_off, int act, float* state, long long slot_stride,
+                             const int* q_start, const int* state_slots, int n_seqs, int n_tokens, int width, int out_bf16, cudaStream_t stream) {
+  if (n_seqs <= 0) return ALOFA_OK;
+  if (width <= 0) return ALOFA_ERR_ARGUMENT;
+  const dim3 grid((width + 31) / 32, n_seqs);
+  // stretches of 16 tokens or more: shorter ones cost more in the (A, B) pass than they save
+  int warps = 1;
+  while (warps < LRU_MAX_WARPS && (long long)n_tokens >= (long long)n_seqs * warps * 2 * 16) warps *= 2;
+  if (out_bf16) launch_dep(lru_scan_kernel<bf16>, grid, warps * 32, 0, stream, (bf16*)out, a, b, y, ldy, y_off, act, state, slot_stride, q_start, state_slots, width);
+  else launch_dep(lru_scan_kernel<float>, grid, warps * 32, 0, stream, (float*)out, a, b, y, ldy, y_off, act, state, slot_stride, q_start, state_slots, width);
+  return launch_status();
+}

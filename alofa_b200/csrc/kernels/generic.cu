@@ -278,13 +278,15 @@ ALOFA_API int alofa_rope_store(void* q_out, void* k_cache, void* v_cache, const 
 // one key, the block takes max and sum in a fixed order, and the value sum is
 // rescaled as in streaming softmax.  score = dot * scale, then (softcap > 0)
 // softcap * tanh(score / softcap), all in fp32.  Keys have hd numbers per head,
-// values vd (the two caches have their own row widths).
+// values vd (the two caches have their own row widths); v_share neighbouring key heads read one value
+// head; chunk > 0: a query sees only the keys of its own chunk of that many positions.
 // ---------------------------------------------------------------------------
-template <typename T>
+template <typename T, typename TO>
 __global__ void __launch_bounds__(128) paged_attention_generic_kernel(
-    T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+    TO* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
-    int max_blocks, int page_size, int nh, int nkv, int hd, int vd, int window, float scale, float softcap, const float* __restrict__ sink) {
+    int max_blocks, int page_size, int nh, int nkv, int hd, int vd, int window, float scale, float softcap, const float* __restrict__ sink,
+    int chunk, int v_share) {
   extern __shared__ float smem[];
   float* qs = smem;          // hd
   float* ps = smem + hd;     // 128
@@ -297,6 +299,8 @@ __global__ void __launch_bounds__(128) paged_attention_generic_kernel(
   for (int d = tid; d < hd; d += 128) qs[d] = to_f(q[((size_t)t * nh + h) * hd + d]);
   int first = 0;
   if (window > 0 && P - window + 1 > 0) first = P - window + 1;
+  if (chunk > 0) first = max(first, P - P % chunk);  // chunks are counted from the sequence's position 0
+  const int vh = kvh / v_share, nv = nkv / v_share;  // v_share neighbouring key heads read one value head
   // a sink is one more term of the softmax's denominator, exp(sink[h]), that belongs to no key and has no value
   float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
   float acc0 = 0.f, acc1 = 0.f;  // dims tid and tid + 128
@@ -329,7 +333,7 @@ __global__ void __launch_bounds__(128) paged_attention_generic_kernel(
     for (int i = 0; i < n_in; ++i) {
       const int sl = pages[i];
       if (sl < 0) continue;
-      const T* vr = v_cache + ((size_t)sl * nkv + kvh) * vd;
+      const T* vr = v_cache + ((size_t)sl * nv + vh) * vd;
       const float pi = ps[i];
       if (tid < vd) acc0 = fmaf(pi, to_f(vr[tid]), acc0);
       if (tid + 128 < vd) acc1 = fmaf(pi, to_f(vr[tid + 128]), acc1);
@@ -337,26 +341,31 @@ __global__ void __launch_bounds__(128) paged_attention_generic_kernel(
     m = m_new;
     __syncthreads();
   }
-  T* o = out + ((size_t)t * nh + h) * vd;
-  if (tid < vd) o[tid] = from_f<T>(acc0 / l);
-  if (tid + 128 < vd) o[tid + 128] = from_f<T>(acc1 / l);
+  TO* o = out + ((size_t)t * nh + h) * vd;
+  if (tid < vd) o[tid] = from_f<TO>(acc0 / l);
+  if (tid + 128 < vd) o[tid + 128] = from_f<TO>(acc1 / l);
 }
 
 ALOFA_API int alofa_paged_attention_generic(void* out, const void* q, const void* k_cache, const void* v_cache,
                                             const int* positions, const int* seq_of_token, const int* block_table,
                                             int max_blocks, int page_size, int n_tokens, int nh, int nkv, int hd,
-                                            int vd, int window, float scale, float softcap, const float* sink, int is_bf16, cudaStream_t stream) {
+                                            int vd, int window, float scale, float softcap, const float* sink, int is_bf16, int chunk, int v_share,
+                                            int out_f32, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
-  if (hd <= 0 || vd <= 0 || vd > 256 || nkv <= 0 || nh % nkv != 0 || page_size <= 0) return ALOFA_ERR_ARGUMENT;
+  if (hd <= 0 || vd <= 0 || vd > 256 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || chunk < 0 || v_share <= 0 || nkv % v_share != 0) return ALOFA_ERR_ARGUMENT;
   dim3 grid(n_tokens, nh);
   const size_t smem = (size_t)(hd + 128) * sizeof(float);
-  if (is_bf16)
-    paged_attention_generic_kernel<bf16><<<grid, 128, smem, stream>>>(
+  if (is_bf16 && out_f32)
+    paged_attention_generic_kernel<bf16, float><<<grid, 128, smem, stream>>>(
+        (float*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, positions, seq_of_token, block_table,
+        max_blocks, page_size, nh, nkv, hd, vd, window, scale, softcap, sink, chunk, v_share);
+  else if (is_bf16)
+    paged_attention_generic_kernel<bf16, bf16><<<grid, 128, smem, stream>>>(
         (bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, positions, seq_of_token, block_table,
-        max_blocks, page_size, nh, nkv, hd, vd, window, scale, softcap, sink);
+        max_blocks, page_size, nh, nkv, hd, vd, window, scale, softcap, sink, chunk, v_share);
   else
-    paged_attention_generic_kernel<float><<<grid, 128, smem, stream>>>(
+    paged_attention_generic_kernel<float, float><<<grid, 128, smem, stream>>>(
         (float*)out, (const float*)q, (const float*)k_cache, (const float*)v_cache, positions, seq_of_token, block_table,
-        max_blocks, page_size, nh, nkv, hd, vd, window, scale, softcap, sink);
+        max_blocks, page_size, nh, nkv, hd, vd, window, scale, softcap, sink, chunk, v_share);
   return launch_status();
 }

@@ -154,6 +154,20 @@ ALOFA_API int alofa_scale_rows(float* x, float scale, long long count, cudaStrea
   return launch_status();
 }
 
+// x = cap * tanh(x / cap) (fp32): logits that the design bounds.
+__global__ void softcap_rows_kernel(float* __restrict__ x, float cap, long long count) {
+  pdl_begin();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) x[i] = cap * tanhf(x[i] / cap);
+}
+
+ALOFA_API int alofa_softcap_rows(float* x, float cap, long long count, cudaStream_t stream) {
+  if (count <= 0) return ALOFA_OK;
+  if (!(cap > 0.f)) return ALOFA_ERR_ARGUMENT;
+  launch_dep(softcap_rows_kernel, (unsigned)((count + 255) / 256), 256, 0, stream, x, cap, count);
+  return launch_status();
+}
+
 // o[t, h, :] *= sigmoid(g[t, g_off + h]): one gate per head from fp32 sums of a projection (row stride ldg); o in the compute dtype.
 template <typename T>
 __global__ void head_gate_kernel(T* __restrict__ o, const float* __restrict__ g, int ldg, int g_off, int heads, int vdim, long long count) {

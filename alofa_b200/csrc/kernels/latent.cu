@@ -426,7 +426,8 @@ ALOFA_API int alofa_latent_attention(void* out, const void* qa, const void* cach
 // ---------------------------------------------------------------------------
 // Sandwich norms.  h (fp32 stream) += rmsnorm(y) * w_post; and, when x is given,
 // x = rmsnorm(h) * w_next of the updated row (the norm ahead of the next
-// sublayer) in the compute dtype.  One block per row, fp32 throughout.
+// sublayer; without w_next the updated row itself) in the compute dtype.  One
+// block per row, fp32 throughout.
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) sandwich_norm_kernel(float* __restrict__ h, const float* __restrict__ y, const float* __restrict__ w_post,
@@ -446,6 +447,10 @@ __global__ void __launch_bounds__(256) sandwich_norm_kernel(float* __restrict__ 
     s2 = fmaf(v, v, s2);
   }
   if (!x) return;
+  if (!w_next) {  // no norm ahead of the next sublayer: it reads the row itself
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) x[r + c] = from_f<T>(h[r + c]);
+    return;
+  }
   s2 = block_sum(s2, scratch);
   const float g = 1.0f / sqrtf(s2 / (float)hidden + eps_next);
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) x[r + c] = from_f<T>(h[r + c] * g * w_next[c]);
@@ -488,13 +493,16 @@ __global__ void __launch_bounds__(256) sandwich_norm_rows_kernel(float* __restri
     }
   }
   if (!x) return;
-  s2 = block_sum(s2, scratch);
-  const float g = 1.0f / sqrtf(s2 / (float)hidden + eps_next);
+  float g = 1.0f;
+  if (w_next) {
+    s2 = block_sum(s2, scratch);
+    g = 1.0f / sqrtf(s2 / (float)hidden + eps_next);
+  }
 #pragma unroll
   for (int i = 0; i < CHUNKS; ++i) {
     const int c = threadIdx.x + 256 * i;
     if (c < quads) {
-      const float4 w = reinterpret_cast<const float4*>(w_next)[c];
+      const float4 w = w_next ? reinterpret_cast<const float4*>(w_next)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
       T* o = x + r + 4 * (size_t)c;
       o[0] = from_f<T>(hv[i].x * g * w.x);
       o[1] = from_f<T>(hv[i].y * g * w.y);
@@ -533,6 +541,21 @@ __global__ void concat_rows_kernel(T* __restrict__ out, const float* __restrict_
     out[t * 2 * hidden + c] = from_f<T>(a[t * hidden + c]);
     out[t * 2 * hidden + hidden + c] = from_f<T>(b[t * hidden + c]);
   }
+}
+
+// out = a, elementwise, from fp32 into the compute dtype: the rows a sublayer reads when no norm stands ahead of it.
+template <typename T>
+__global__ void cast_rows_kernel(T* __restrict__ out, const float* __restrict__ a, long long count) {
+  pdl_begin();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) out[i] = from_f<T>(a[i]);
+}
+
+ALOFA_API int alofa_cast_rows(void* out, const float* a, long long count, int out_bf16, cudaStream_t stream) {
+  if (count <= 0) return ALOFA_OK;
+  if (out_bf16) launch_dep(cast_rows_kernel<bf16>, (unsigned)((count + 255) / 256), 256, 0, stream, (bf16*)out, a, count);
+  else launch_dep(cast_rows_kernel<float>, (unsigned)((count + 255) / 256), 256, 0, stream, (float*)out, a, count);
+  return launch_status();
 }
 
 ALOFA_API int alofa_concat_rows(void* out, const float* a, const float* b, int rows, int hidden, int out_bf16, cudaStream_t stream) {
@@ -608,11 +631,12 @@ template <typename T, int TT>
 __global__ void __launch_bounds__(256) moe_router_kernel(int* __restrict__ choice, float* __restrict__ weight, float* __restrict__ gate,
                                                          const T* __restrict__ x, const float* __restrict__ wr, int T_, int E, int top, int hidden,
                                                          int gated, int softmax, int renormalize, const float* __restrict__ correction,
-                                                         float renorm_eps) {
+                                                         float renorm_eps, int groups, int keep, float route_scale) {
   extern __shared__ __align__(16) uint8_t router_smem[];
   const int cols = E + (gated ? 1 : 0);
   float* z = reinterpret_cast<float*>(router_smem);      // [TT][cols]
-  T* xs = reinterpret_cast<T*>(z + ((TT * cols + 3) & ~3));  // [TT][hidden], on a 16-byte boundary
+  float* gsc = z + TT * cols;                            // [TT][groups]: the groups' scores
+  T* xs = reinterpret_cast<T*>(z + ((TT * (cols + groups) + 3) & ~3));  // [TT][hidden], on a 16-byte boundary
   pdl_begin();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t0 = blockIdx.x * TT;
@@ -679,6 +703,30 @@ __global__ void __launch_bounds__(256) moe_router_kernel(int* __restrict__ choic
       for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
     }
     __syncwarp();
+    if (groups > 1) {
+      // experts form `groups` equal groups of neighbours; a group's score is the sum of its two largest choice
+      // scores (score + correction); only experts of the `keep` best groups can be chosen (ties: the lower group)
+      const int per = E / groups;
+      float* gs = gsc + r * groups;
+      for (int g = lane; g < groups; g += 32) {
+        float a = -INFINITY, b = -INFINITY;  // the largest and the second
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+          const float v = correction ? s[e] + correction[e] : s[e];
+          if (v > a) b = a, a = v;
+          else if (v > b) b = v;
+        }
+        gs[g] = per > 1 ? a + b : a;
+      }
+      __syncwarp();
+      for (int g = lane; g < groups; g += 32) {
+        const float mine = gs[g];
+        int ahead = 0;
+        for (int o = 0; o < groups; ++o) ahead += (gs[o] > mine || (gs[o] == mine && o < g)) ? 1 : 0;
+        if (ahead >= keep)
+          for (int e = g * per; e < (g + 1) * per; ++e) s[e] = -INFINITY;  // never the largest: score + correction stays -inf
+      }
+      __syncwarp();
+    }
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
       // the choice goes by score + correction (when given), the weight is the score itself
@@ -705,40 +753,46 @@ __global__ void __launch_bounds__(256) moe_router_kernel(int* __restrict__ choic
       total += best;
       __syncwarp();
     }
-    if (renormalize && lane < top) weight[(size_t)t * top + lane] /= total + renorm_eps;
+    if (renormalize && lane < top) weight[(size_t)t * top + lane] = weight[(size_t)t * top + lane] / (total + renorm_eps) * route_scale;
+    else if (route_scale != 1.0f && lane < top) weight[(size_t)t * top + lane] *= route_scale;
     if (gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-zg));
   }
 }
 
 template <typename T, int TT>
 static int moe_router_launch(int* choice, float* weight, float* gate, const void* x, const float* wr, int T_, int E, int top, int hidden, int softmax,
-                             int renormalize, const float* correction, float renorm_eps, cudaStream_t stream) {
+                             int renormalize, const float* correction, float renorm_eps, int groups, int keep, float route_scale, cudaStream_t stream) {
   const int cols = E + (gate ? 1 : 0);
-  const size_t smem = ((size_t)TT * cols + 4) * sizeof(float) + (size_t)TT * hidden * sizeof(T);
+  const size_t smem = ((size_t)TT * (cols + groups) + 4) * sizeof(float) + (size_t)TT * hidden * sizeof(T);
   static size_t set = 0;
   if (smem > set) {
     if (cudaFuncSetAttribute(moe_router_kernel<T, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
     set = smem;
   }
   launch_dep(moe_router_kernel<T, TT>, (T_ + TT - 1) / TT, 256, smem, stream, choice, weight, gate, (const T*)x, wr, T_, E, top, hidden, gate ? 1 : 0, softmax,
-             renormalize, correction, renorm_eps);
+             renormalize, correction, renorm_eps, groups, keep, route_scale);
   return launch_status();
 }
 
 // correction (optional, fp32 [E]): added to the scores for the choice only.  renorm_eps: added to the sum the weights are divided by.
+// groups > 1: the experts form that many equal groups of neighbours, of which only the `keep` best (by the sum of their two largest
+// choice scores) can be chosen.  route_scale: a factor on the weights.
 ALOFA_API int alofa_moe_router(int* choice, float* weight, float* gate, const void* x, const float* wr, int T, int E, int top, int hidden, int softmax,
-                               int renormalize, int x_bf16, const float* correction, float renorm_eps, cudaStream_t stream) {
+                               int renormalize, int x_bf16, const float* correction, float renorm_eps, int groups, int keep, float route_scale,
+                               cudaStream_t stream) {
   if (T <= 0) return ALOFA_OK;
   if (E <= 0 || top <= 0 || top > E || top > 32) return ALOFA_ERR_ARGUMENT;
-  const size_t row = (size_t)hidden * (x_bf16 ? 2 : 4) + (size_t)(E + 1) * 4;
+  if (groups < 1) groups = 1;
+  if (groups > 1 && (E % groups || keep < 1 || keep > groups || keep * (E / groups) < top)) return ALOFA_ERR_ARGUMENT;
+  const size_t row = (size_t)hidden * (x_bf16 ? 2 : 4) + (size_t)(E + groups + 1) * 4;
   const size_t room = 200 * 1024;
   // few tokens: two to a block, so that a decode step's tokens are spread over more than a handful of SMs
   if (8 * row <= room && T > 512)
-    return x_bf16 ? moe_router_launch<bf16, 8>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, correction, renorm_eps, stream)
-                  : moe_router_launch<float, 8>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, correction, renorm_eps, stream);
+    return x_bf16 ? moe_router_launch<bf16, 8>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, correction, renorm_eps, groups, keep, route_scale, stream)
+                  : moe_router_launch<float, 8>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, correction, renorm_eps, groups, keep, route_scale, stream);
   if (2 * row <= room)
-    return x_bf16 ? moe_router_launch<bf16, 2>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, correction, renorm_eps, stream)
-                  : moe_router_launch<float, 2>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, correction, renorm_eps, stream);
+    return x_bf16 ? moe_router_launch<bf16, 2>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, correction, renorm_eps, groups, keep, route_scale, stream)
+                  : moe_router_launch<float, 2>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, correction, renorm_eps, groups, keep, route_scale, stream);
   return ALOFA_ERR_ARGUMENT;
 }
 

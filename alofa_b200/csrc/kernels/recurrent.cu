@@ -68,8 +68,8 @@ ALOFA_API int alofa_add_rows(float* out, const float* x, long long count, cudaSt
 }
 
 // ---------------------------------------------------------------------------
-// Causal convolution per channel with an activation: for channel c of the token at place j of its
-// request, out = silu(bias[c] + sum_l w[c, taps - 1 - l] * in(j - l)), l = 0 .. taps - 1 (the last
+// Causal convolution per channel with an activation (act 1: silu, 0: none): for channel c of the token at place j of its
+// request, out = act(bias[c] + sum_l w[c, taps - 1 - l] * in(j - l)), l = 0 .. taps - 1 (the last
 // column of w belongs to the token itself).  Inputs before the step's first token come from the
 // request's state, which holds its last taps - 1 inputs (the newest last; zeros before a request's
 // start).  u [T, ld] fp32, the channels at columns offset ..; out [T, channels] fp32.
@@ -77,7 +77,7 @@ ALOFA_API int alofa_add_rows(float* out, const float* x, long long count, cudaSt
 __global__ void __launch_bounds__(256) causal_conv_kernel(float* __restrict__ out, const float* __restrict__ u, int ld, int offset, const float* __restrict__ w,
                                                           const float* __restrict__ bias, const float* __restrict__ state, long long slot_stride,
                                                           const int* __restrict__ q_start, const int* __restrict__ state_slots,
-                                                          const int* __restrict__ seq_of_token, int channels, int taps) {
+                                                          const int* __restrict__ seq_of_token, int channels, int taps, int act) {
   pdl_begin();
   const int t = blockIdx.x, c = blockIdx.y * 256 + threadIdx.x;
   if (c >= channels) return;
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(float* __restrict__ ou
     const float v = jj >= 0 ? u[(size_t)(t - l) * ld + offset + c] : st[(size_t)(taps - 1 + jj) * channels + c];
     acc = fmaf(w[(size_t)c * taps + taps - 1 - l], v, acc);
   }
-  out[(size_t)t * channels + c] = silu_f(acc);
+  out[(size_t)t * channels + c] = act ? silu_f(acc) : acc;
 }
 
 // The state after the step: the last taps - 1 inputs of each request.  One thread per (request,
@@ -112,11 +112,11 @@ __global__ void __launch_bounds__(256) conv_state_kernel(float* __restrict__ sta
 
 ALOFA_API int alofa_causal_conv(float* out, const float* u, int ld, int offset, const float* w, const float* bias, float* state, long long slot_stride,
                                 const int* q_start, const int* state_slots, const int* seq_of_token, int n_tokens, int n_seqs, int channels, int taps,
-                                cudaStream_t stream) {
+                                int act, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
   if (channels <= 0 || taps <= 0) return ALOFA_ERR_ARGUMENT;
   launch_dep(causal_conv_kernel, dim3(n_tokens, (channels + 255) / 256), 256, 0, stream, out, u, ld, offset, w, bias, (const float*)state, slot_stride, q_start,
-             state_slots, seq_of_token, channels, taps);
+             state_slots, seq_of_token, channels, taps, act);
   if (taps > 1)
     launch_dep(conv_state_kernel, dim3(n_seqs, (channels + 255) / 256), 256, 0, stream, state, slot_stride, u, ld, offset, q_start, state_slots, channels, taps);
   return launch_status();
@@ -471,25 +471,29 @@ ALOFA_API int alofa_branch_norm_add(float* h, const float* ya, const float* wa, 
 }
 
 // ---------------------------------------------------------------------------
-// Queries, keys and values of softmax attention without rotation, from the fp32 sums of one stacked
-// projection [q: H * d | k: G * d | v: G * dv]:  q and k divided by their root mean square over
-// d per head (qk_norm; no weight), q times 1 + coef * ln(floor((p + 1) / every) + 1) at position p
-// (coef != 0), q to its own buffer, k and v to the token's cache slot.  A warp per (token, head).
+// Queries, keys and values of softmax attention from the fp32 sums of one stacked projection, a row of ld
+// numbers that starts [q: H * maps * d | k: G * maps * d | v: G * dv] (v_from_k: no v columns, the values
+// are the keys as projected, before their norm).  With maps > 1 a head has several queries and a key head
+// several keys, side by side ([map 1, map 2] per head): softmax maps of their own over the same values.
+// q and k divided by their root mean square over d per head and map (qk_norm), times a weight of d
+// numbers (q_w, k_w; may be absent); q times 1 + coef * ln(floor((p + 1) / every) + 1) at position p
+// (coef != 0); the first rot_dims numbers turned in neighbouring pairs; q to its own buffer, k and v to
+// the token's cache slot.  A warp per (token, head and map).
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256) qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const float* __restrict__ qkv,
-                                                          const int* __restrict__ positions, const int* __restrict__ slot_map, int H, int G, int d, int dv,
-                                                          int qk_norm, float eps, float coef, int every, int n_tokens,
-                                                          const float* __restrict__ freq, int rot_dims) {
+__global__ void __launch_bounds__(256) qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const float* __restrict__ qkv, int ld,
+                                                          const int* __restrict__ positions, const int* __restrict__ slot_map, int H, int G, int d, int dv, int maps,
+                                                          int qk_norm, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps, float coef, int every,
+                                                          int n_tokens, const float* __restrict__ freq, int rot_dims, float mag, int v_from_k) {
   pdl_begin();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int per = H + 2 * G;
+  const int HQ = H * maps, GK = G * maps;
+  const int per = HQ + GK + G;
   const long long unit = (long long)blockIdx.x * 8 + warp;
   if (unit >= (long long)n_tokens * per) return;
   const int t = (int)(unit / per), u = (int)(unit - (long long)t * per);
-  const int ld = H * d + G * d + G * dv;
   const float* row = qkv + (size_t)t * ld;
-  if (u < H + G) {
+  if (u < HQ + GK) {
     const float* x = row + (size_t)u * d;
     float mul = 1.f;
     if (qk_norm) {
@@ -499,45 +503,107 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(T* __restrict__ q_out,
       mul = 1.0f / sqrtf(ss / (float)d + eps);
     }
     T* to;
-    if (u < H) {
+    const float* w;
+    if (u < HQ) {
       if (coef != 0.f) mul *= 1.0f + coef * logf((float)((positions[t] + 1) / every) + 1.0f);
-      to = q_out + ((size_t)t * H + u) * d;
+      // head h's map m goes where the heads of its key head's group lie side by side: [key head][map][head of the group]
+      const int h = u / maps, m = u - h * maps, hg = H / G;
+      const int g = h / hg, hh = h - g * hg;
+      to = q_out + ((size_t)t * HQ + (size_t)(g * maps + m) * hg + hh) * d;
+      w = q_w;
     } else {
-      to = k_cache + ((size_t)slot_map[t] * G + (u - H)) * d;
+      to = k_cache + ((size_t)slot_map[t] * GK + (u - HQ)) * d;
+      w = k_w;
     }
     if (rot_dims > 0) {
-      // neighbouring pairs (2i, 2i + 1), i < rot_dims / 2, turned by the angle p * freq[i] (an fp32 product, precise sine and cosine)
+      // neighbouring pairs (2i, 2i + 1), i < rot_dims / 2, turned by the angle p * freq[i] (an fp32 product, precise sine and cosine),
+      // cosine and sine times mag
       const float p = (float)positions[t];
       for (int i = lane; i < rot_dims / 2; i += 32) {
         float sn, cs;
         sincosf(p * freq[i], &sn, &cs);
-        const float a = x[2 * i] * mul, b = x[2 * i + 1] * mul;
+        sn *= mag;
+        cs *= mag;
+        float a = x[2 * i] * mul, b = x[2 * i + 1] * mul;
+        if (w) a *= w[2 * i], b *= w[2 * i + 1];
         to[2 * i] = from_f<T>(a * cs - b * sn);
         to[2 * i + 1] = from_f<T>(b * cs + a * sn);
       }
     }
-    for (int c = rot_dims + lane; c < d; c += 32) to[c] = from_f<T>(x[c] * mul);
+    if (w) for (int c = rot_dims + lane; c < d; c += 32) to[c] = from_f<T>(x[c] * mul * w[c]);
+    else for (int c = rot_dims + lane; c < d; c += 32) to[c] = from_f<T>(x[c] * mul);
   } else {
-    const int gi = u - H - G;
-    const float* x = row + (size_t)(H + G) * d + (size_t)gi * dv;
+    const int gi = u - HQ - GK;
+    // the values: their own columns, or (v_from_k) the keys as projected, before their norm
+    const float* x = v_from_k ? row + (size_t)HQ * d + (size_t)gi * d : row + (size_t)(HQ + GK) * d + (size_t)gi * dv;
     T* to = v_cache + ((size_t)slot_map[t] * G + gi) * dv;
     for (int c = lane; c < dv; c += 32) to[c] = from_f<T>(x[c]);
   }
 }
 
-ALOFA_API int alofa_qkv_prepare(void* q_out, void* k_cache, void* v_cache, const float* qkv, const int* positions, const int* slot_map, int n_tokens, int H, int G,
-                                int d, int dv, int qk_norm, float eps, float coef, int every, const float* freq, int rot_dims, int is_bf16,
-                                cudaStream_t stream) {
+ALOFA_API int alofa_qkv_prepare(void* q_out, void* k_cache, void* v_cache, const float* qkv, int ld, const int* positions, const int* slot_map, int n_tokens, int H, int G,
+                                int d, int dv, int maps, int qk_norm, const float* q_w, const float* k_w, float eps, float coef, int every, const float* freq,
+                                int rot_dims, float mag, int v_from_k, int is_bf16, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
-  if (H <= 0 || G <= 0 || d <= 0 || dv <= 0 || (coef != 0.f && every <= 0) || rot_dims < 0 || rot_dims > d || (rot_dims & 1) || (rot_dims && !freq))
+  if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || maps <= 0 || (coef != 0.f && every <= 0) || rot_dims < 0 || rot_dims > d || (rot_dims & 1) || (rot_dims && !freq) ||
+      (v_from_k && (maps != 1 || dv != d)) || ld < (H + G) * maps * d + (v_from_k ? 0 : G * dv))
     return ALOFA_ERR_ARGUMENT;
-  const long long units = (long long)n_tokens * (H + 2 * G);
+  const long long units = (long long)n_tokens * ((H + G) * maps + G);
   const unsigned blocks = (unsigned)((units + 7) / 8);
   if (is_bf16)
-    launch_dep(qkv_prepare_kernel<bf16>, blocks, 256, 0, stream, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, qkv, positions, slot_map, H, G, d, dv, qk_norm, eps, coef,
-               every, n_tokens, freq, rot_dims);
+    launch_dep(qkv_prepare_kernel<bf16>, blocks, 256, 0, stream, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, qkv, ld, positions, slot_map, H, G, d, dv, maps, qk_norm,
+               q_w, k_w, eps, coef, every, n_tokens, freq, rot_dims, mag, v_from_k);
   else
-    launch_dep(qkv_prepare_kernel<float>, blocks, 256, 0, stream, (float*)q_out, (float*)k_cache, (float*)v_cache, qkv, positions, slot_map, H, G, d, dv, qk_norm, eps,
-               coef, every, n_tokens, freq, rot_dims);
+    launch_dep(qkv_prepare_kernel<float>, blocks, 256, 0, stream, (float*)q_out, (float*)k_cache, (float*)v_cache, qkv, ld, positions, slot_map, H, G, d, dv, maps,
+               qk_norm, q_w, k_w, eps, coef, every, n_tokens, freq, rot_dims, mag, v_from_k);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// heads_finish: what some attentions do to a head's output before the output projection, one warp per
+// (token, head), fp32.  a [T, H * maps, dv] fp32 holds the attention outputs in the order qkv_prepare
+// gave the queries ([key head][map][head of the group]).
+//   maps 1: o = a
+//   maps 2: o = a_1 - lambda * a_2, then o / sqrt(mean(o^2) + eps) * post   (two softmax maps over the same values)
+//   gate:   o *= sigmoid(gate[t, g_off + h])   (fp32 sums of a projection, row stride ldg)
+// out [T, H * dv] in the compute dtype, heads in their own order.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) heads_finish_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ gate, int ldg, int g_off,
+                                                           int H, int G, int dv, int maps, float lambda, float eps, float post, long long units) {
+  pdl_begin();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 8 + warp;
+  if (unit >= units) return;
+  const long long t = unit / H;
+  const int h = (int)(unit - t * H), hg = H / G;
+  const int g = h / hg, hh = h - g * hg;
+  const float* a1 = a + ((size_t)t * H * maps + (size_t)(g * maps) * hg + hh) * dv;
+  T* o = out + ((size_t)t * H + h) * dv;
+  float f = 1.f;
+  if (gate) f = 1.0f / (1.0f + expf(-gate[t * ldg + g_off + h]));
+  if (maps == 1) {
+    for (int c = lane; c < dv; c += 32) o[c] = from_f<T>(a1[c] * f);
+    return;
+  }
+  const float* a2 = a1 + (size_t)hg * dv;
+  float ss = 0.f;
+  for (int c = lane; c < dv; c += 32) {
+    const float v = a1[c] - lambda * a2[c];
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  const float r = post / sqrtf(ss / (float)dv + eps);
+  for (int c = lane; c < dv; c += 32) o[c] = from_f<T>((a1[c] - lambda * a2[c]) * r * f);
+}
+
+ALOFA_API int alofa_heads_finish(void* out, const float* a, const float* gate, int ldg, int g_off, int n_tokens, int H, int G, int dv, int maps, float lambda, float eps,
+                                 float post, int is_bf16, cudaStream_t stream) {
+  if (n_tokens <= 0) return ALOFA_OK;
+  if (H <= 0 || G <= 0 || H % G || dv <= 0 || maps < 1 || maps > 2) return ALOFA_ERR_ARGUMENT;
+  const long long units = (long long)n_tokens * H;
+  const unsigned blocks = (unsigned)((units + 7) / 8);
+  if (is_bf16) launch_dep(heads_finish_kernel<bf16>, blocks, 256, 0, stream, (bf16*)out, a, gate, ldg, g_off, H, G, dv, maps, lambda, eps, post, units);
+  else launch_dep(heads_finish_kernel<float>, blocks, 256, 0, stream, (float*)out, a, gate, ldg, g_off, H, G, dv, maps, lambda, eps, post, units);
   return launch_status();
 }

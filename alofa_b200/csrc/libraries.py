@@ -11,6 +11,7 @@ def all_libraries() -> list:
         {"name": "alofa_latent", "sources": ["kernels/latent.cu", "kernels/gemm_batched_bf16.cu"]},
         {"name": "alofa_recurrent", "sources": ["kernels/recurrent.cu"]},
         {"name": "alofa_delta", "sources": ["kernels/delta.cu"]},
+        {"name": "alofa_gated_lru", "sources": ["kernels/gated_lru.cu"]},
         {"name": "alofa_hyper", "sources": ["kernels/hyper.cu"]},
         {"name": "alofa_sampling", "sources": ["kernels/sampling.cu"]},
         {"name": "alofa_gemm_tc", "sources": ["kernels/gemm_tc.cu"]},

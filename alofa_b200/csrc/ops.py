@@ -41,7 +41,7 @@ def _generic():
             "alofa_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _P],
             "alofa_gemm_generic": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
             "alofa_rope_store": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-            "alofa_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P, _I, _P],
+            "alofa_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P, _I, _I, _I, _I, _P],
         }
         for name, args in sigs.items():
             fn = getattr(lib, name)
@@ -265,24 +265,30 @@ def rope_store(q_out, k_cache, v_cache, qkv, cos_sin, positions, slot_map, nh, n
     )
 
 
-def paged_attention_generic(out, q, k_cache, v_cache, positions, seq_of_token, block_table, page_size, nh, nkv, hd, window, scale, softcap: float = 0.0, vd=None, sink=None) -> None:
+def paged_attention_generic(out, q, k_cache, v_cache, positions, seq_of_token, block_table, page_size, nh, nkv, hd, window, scale, softcap: float = 0.0, vd=None, sink=None,
+                            chunk: int = 0, v_share: int = 1) -> None:
     """Causal grouped-query attention over the paged cache for every size and
     both dtypes; fp32 scores and softmax.  ``softcap`` > 0 bounds the scaled
     scores by ``softcap * tanh(score / softcap)``; ``vd`` is the values' head
     size when it differs from the keys' ``hd``; ``sink`` (fp32, one score per
     head) adds ``exp(sink[h])`` to the softmax's denominator, a term that
-    belongs to no key and has no value."""
+    belongs to no key and has no value.  ``chunk`` > 0: a query at position p
+    sees only the keys from ``p - p % chunk`` on.  ``v_share``: so many
+    neighbouring key heads read one value head (the value cache has ``nkv /
+    v_share`` heads).  ``out`` may be fp32 while q and the caches are
+    bfloat16."""
     n = q.shape[0]
     vd = hd if vd is None else vd
     dt = q.dtype
-    if tuple(k_cache.shape[1:]) != (nkv, hd) or tuple(v_cache.shape[1:]) != (nkv, vd) or tuple(q.shape) != (n, nh * hd) or tuple(out.shape) != (n, nh * vd):
+    if (tuple(k_cache.shape[1:]) != (nkv, hd) or nkv % v_share or tuple(v_cache.shape[1:]) != (nkv // v_share, vd) or tuple(q.shape) != (n, nh * hd)
+            or tuple(out.shape) != (n, nh * vd) or out.dtype not in (dt, torch.float32)):
         raise AlofaError("invalid_argument", "attention sizes disagree", f"q={tuple(q.shape)} out={tuple(out.shape)} k={tuple(k_cache.shape)} v={tuple(v_cache.shape)}")
     _done(
         _generic().alofa_paged_attention_generic(
-            _dev(out, "out", dt), _dev(q, "q"), _dev(k_cache, "k_cache", dt), _dev(v_cache, "v_cache", dt),
+            _dev(out, "out"), _dev(q, "q"), _dev(k_cache, "k_cache", dt), _dev(v_cache, "v_cache", dt),
             _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32), _dev(block_table, "block_table", torch.int32),
             block_table.shape[1], page_size, n, nh, nkv, hd, vd, int(window or 0), float(scale), float(softcap or 0.0),
-            _dev(sink, "sink", torch.float32) if sink is not None else None, _is_bf16(q, "q"), _stream(),
+            _dev(sink, "sink", torch.float32) if sink is not None else None, _is_bf16(q, "q"), int(chunk or 0), int(v_share), 1 if out.dtype == torch.float32 else 0, _stream(),
         ),
         "paged_attention_generic", f"heads={nh} kv_heads={nkv} head_dim={hd} v_head_dim={vd}",
     )
@@ -578,7 +584,8 @@ def _latent():
             "alofa_sandwich_norm": [_P, _P, _P, _F, _P, _P, _F, _I, _I, _I, _P],
             "alofa_concat_rows": [_P, _P, _P, _I, _I, _I, _P],
             "alofa_moe_route": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-            "alofa_moe_router": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _F, _P],
+            "alofa_moe_router": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _F, _I, _I, _F, _P],
+            "alofa_cast_rows": [_P, _P, _L, _I, _P],
             "alofa_moe_sort": [_P, _P, _P, _I, _I, _I, _I, _P],
             "alofa_moe_scatter": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
             "alofa_moe_combine": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _I, _I, _P],
@@ -713,16 +720,24 @@ def latent_attention(out, qa, cache_rows, sink, positions, seq_of_token, block_t
 
 def sandwich_norm(h, y, w_post, eps_post: float, x=None, w_next=None, eps_next: float = 0.0) -> None:
     """``h += rmsnorm(y) * w_post`` (fp32 stream); with ``x`` also ``x =
-    rmsnorm(h) * w_next`` of the updated rows, in x's dtype."""
+    rmsnorm(h) * w_next`` of the updated rows (without ``w_next``: the updated
+    rows themselves), in x's dtype."""
     rows, hidden = h.shape
     if tuple(y.shape) != (rows, hidden) or (x is not None and tuple(x.shape) != (rows, hidden)):
         raise AlofaError("invalid_argument", "sandwich_norm sizes disagree", f"h={tuple(h.shape)} y={tuple(y.shape)}")
     f32 = torch.float32
     _done(
         _latent().alofa_sandwich_norm(_dev(h, "h", f32), _dev(y, "y", f32), _dev(w_post, "w_post", f32), float(eps_post), _dev(x, "x") if x is not None else None,
-                                      _dev(w_next, "w_next", f32) if x is not None else None, float(eps_next), rows, hidden, _is_bf16(x, "x") if x is not None else 0, _stream()),
+                                      _dev(w_next, "w_next", f32) if x is not None and w_next is not None else None, float(eps_next), rows, hidden, _is_bf16(x, "x") if x is not None else 0, _stream()),
         "sandwich_norm",
     )
+
+
+def cast_rows(out, a) -> None:
+    """out = a (fp32) in out's dtype, same shape."""
+    if out.shape != a.shape:
+        raise AlofaError("invalid_argument", "cast_rows sizes disagree", f"out={tuple(out.shape)} a={tuple(a.shape)}")
+    _done(_latent().alofa_cast_rows(_dev(out, "out"), _dev(a, "a", torch.float32), out.numel(), _is_bf16(out, "out"), _stream()), "cast_rows")
 
 
 def concat_rows(out, a, b) -> None:
@@ -780,20 +795,25 @@ def moe_route(choice, weight, gate, z, experts: int, top: int, softmax: bool = F
 
 
 def moe_router(choice, weight, gate, x, wr, experts: int, top: int, softmax: bool = False, renormalize: bool = False, correction=None,
-               renorm_eps: float = 0.0) -> None:
+               renorm_eps: float = 0.0, groups: int = 1, keep: int = 1, route_scale: float = 1.0) -> None:
     """:func:`moe_route` with the router's product in the same kernel: ``x``
     [T, hidden] in the compute dtype, ``wr`` fp32 [experts (+1 with ``gate``),
     hidden]; logits and scores are fp32.  ``correction`` (fp32 [experts]) is
     added to the scores for the choice only, the weights stay the scores;
-    ``renorm_eps`` is added to the sum that ``renormalize`` divides by."""
+    ``renorm_eps`` is added to the sum that ``renormalize`` divides by.
+    ``groups`` > 1: the experts form that many equal groups of neighbours; a
+    group's score is the sum of its two largest choice scores (score +
+    correction), and only experts of the ``keep`` best groups can be chosen.
+    ``route_scale``: a factor on the weights."""
     i32, f32 = torch.int32, torch.float32
     if wr.shape != (experts + (1 if gate is not None else 0), x.shape[1]) or (correction is not None and correction.shape[0] != experts):
         raise AlofaError("invalid_argument", "router sizes disagree", f"wr={tuple(wr.shape)} x={tuple(x.shape)} experts={experts}")
     _done(
         _latent().alofa_moe_router(_dev(choice, "choice", i32), _dev(weight, "weight", f32), _dev(gate, "gate", f32) if gate is not None else None, _dev(x, "x"),
                                    _dev(wr, "wr", f32), x.shape[0], experts, top, x.shape[1], 1 if softmax else 0, 1 if renormalize else 0, _is_bf16(x, "x"),
-                                   _dev(correction, "correction", f32) if correction is not None else None, float(renorm_eps), _stream()),
-        "moe_router", f"experts={experts} top={top}",
+                                   _dev(correction, "correction", f32) if correction is not None else None, float(renorm_eps), int(groups), int(keep), float(route_scale),
+                                   _stream()),
+        "moe_router", f"experts={experts} top={top} groups={groups} keep={keep}",
     )
 
 
@@ -893,11 +913,12 @@ def _recurrent():
         sigs = {
             "alofa_embed_scaled": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
             "alofa_add_rows": [_P, _P, _L, _P],
-            "alofa_causal_conv": [_P, _P, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _P],
+            "alofa_causal_conv": [_P, _P, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
             "alofa_linear_scan": [_P, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _F, _F, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
             "alofa_gated_group_norm": [_P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P],
             "alofa_branch_norm_add": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _P],
-            "alofa_qkv_prepare": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _I, _I, _P],
+            "alofa_qkv_prepare": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _F, _I, _P, _I, _F, _I, _I, _P],
+            "alofa_heads_finish": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _I, _P],
         }
         for name, args in sigs.items():
             fn = getattr(lib, name)
@@ -933,8 +954,8 @@ def add_rows(out, x) -> None:
     _done(_recurrent().alofa_add_rows(_dev(out, "out", torch.float32), _dev(x, "x", torch.float32), out.numel(), _stream()), "add_rows")
 
 
-def causal_conv(out, u, offset: int, w, bias, state, q_start, state_slots, seq_of_token, n_seqs: int) -> None:
-    """out [T, C] = silu(bias + causal convolution per channel) of the columns
+def causal_conv(out, u, offset: int, w, bias, state, q_start, state_slots, seq_of_token, n_seqs: int, act: bool = True) -> None:
+    """out [T, C] = silu(bias + causal convolution per channel) (``act`` False: no silu) of the columns
     ``offset .. offset + C`` of u [T, ld] (fp32), w [C, taps] fp32 with the
     token's own tap last; ``state`` [slots, >= (taps - 1) * C] fp32 holds each
     request's last taps - 1 inputs and is brought up to date."""
@@ -949,7 +970,7 @@ def causal_conv(out, u, offset: int, w, bias, state, q_start, state_slots, seq_o
         _recurrent().alofa_causal_conv(
             _dev(out, "out", f32), _dev(u, "u", f32), u.shape[1], offset, _dev(w, "w", f32), _dev(bias, "bias", f32) if bias is not None else None,
             state.data_ptr(), state.stride(0), _dev(q_start, "q_start", i32), _dev(state_slots, "state_slots", i32), _dev(seq_of_token, "seq_of_token", i32),
-            n, n_seqs, channels, taps, _stream(),
+            n, n_seqs, channels, taps, 1 if act else 0, _stream(),
         ),
         "causal_conv", f"channels={channels} taps={taps}",
     )
@@ -1031,24 +1052,51 @@ def branch_norm_add(h, ya, wa, yb, wb, eps: float, scale: float) -> None:
 
 
 def qkv_prepare(q_out, k_cache, v_cache, qkv, positions, slot_map, heads: int, kv_heads: int, d: int, dv: int, qk_norm: bool, eps: float, coef: float, every: int,
-                freq=None, rot_dims: int = 0) -> None:
-    """From the fp32 sums of a stacked projection [q | k | v]: q and k divided
-    by their root mean square per head (``qk_norm``), q times ``1 + coef *
-    ln(floor((p + 1) / every) + 1)`` at position p, the first ``rot_dims``
-    numbers of every q and k head turned by the position (neighbouring pairs,
-    pair i by the angle ``p * freq[i]``), q to ``q_out``, k and v to the
-    tokens' cache slots; out tensors in the compute dtype."""
+                freq=None, rot_dims: int = 0, maps: int = 1, q_weight=None, k_weight=None, magnitude: float = 1.0, values_from_keys: bool = False) -> None:
+    """From the fp32 sums of a stacked projection whose rows start [q | k | v]
+    (more columns may follow): q and k divided by their root mean square per
+    head (``qk_norm``) and multiplied by ``q_weight`` / ``k_weight`` (fp32
+    [d], may be None), q times ``1 + coef * ln(floor((p + 1) / every) + 1)`` at
+    position p, the first ``rot_dims`` numbers of every q and k head turned by
+    the position (neighbouring pairs, pair i by the angle ``p * freq[i]``,
+    cosine and sine times ``magnitude``), q to ``q_out``, k and v to the
+    tokens' cache slots; out tensors in the compute dtype.  ``maps`` > 1: every
+    head has that many queries and every key head that many keys, side by side
+    per head; the queries are written as ``[key head][map][head of the
+    group]``, so that a kernel which gives query unit ``i`` the key unit ``i //
+    (heads / kv_heads)`` pairs map with map.  ``values_from_keys``: there are
+    no v columns, the values are the keys as projected (before their norm)."""
     n = qkv.shape[0]
     dt = q_out.dtype
-    if qkv.shape[1] != heads * d + kv_heads * (d + dv) or tuple(q_out.shape) != (n, heads * d) or tuple(k_cache.shape[1:]) != (kv_heads, d) or tuple(v_cache.shape[1:]) != (kv_heads, dv):
+    f32 = torch.float32
+    need = (heads + kv_heads) * maps * d + (0 if values_from_keys else kv_heads * dv)
+    if (qkv.shape[1] < need or tuple(q_out.shape) != (n, heads * maps * d) or tuple(k_cache.shape[1:]) != (kv_heads * maps, d) or tuple(v_cache.shape[1:]) != (kv_heads, dv)
+            or (q_weight is not None and q_weight.shape[0] != d) or (k_weight is not None and k_weight.shape[0] != d)):
         raise AlofaError("invalid_argument", "qkv_prepare sizes disagree", f"qkv={tuple(qkv.shape)} q={tuple(q_out.shape)} k={tuple(k_cache.shape)} v={tuple(v_cache.shape)}")
     _done(
-        _recurrent().alofa_qkv_prepare(_dev(q_out, "q_out"), _dev(k_cache, "k_cache", dt), _dev(v_cache, "v_cache", dt), _dev(qkv, "qkv", torch.float32),
-                                       _dev(positions, "positions", torch.int32), _dev(slot_map, "slot_map", torch.int32), n, heads, kv_heads, d, dv,
-                                       1 if qk_norm else 0, float(eps), float(coef), int(every),
-                                       _dev(freq, "freq", torch.float32) if rot_dims else None, int(rot_dims), _is_bf16(q_out, "q_out"), _stream()),
-        "qkv_prepare",
+        _recurrent().alofa_qkv_prepare(_dev(q_out, "q_out"), _dev(k_cache, "k_cache", dt), _dev(v_cache, "v_cache", dt), _dev(qkv, "qkv", f32), qkv.shape[1],
+                                       _dev(positions, "positions", torch.int32), _dev(slot_map, "slot_map", torch.int32), n, heads, kv_heads, d, dv, int(maps),
+                                       1 if qk_norm else 0, _dev(q_weight, "q_weight", f32) if q_weight is not None else None,
+                                       _dev(k_weight, "k_weight", f32) if k_weight is not None else None, float(eps), float(coef), int(every),
+                                       _dev(freq, "freq", f32) if rot_dims else None, int(rot_dims), float(magnitude), 1 if values_from_keys else 0,
+                                       _is_bf16(q_out, "q_out"), _stream()),
+        "qkv_prepare", f"heads={heads} kv_heads={kv_heads} d={d} dv={dv} maps={maps}",
     )
+
+
+def heads_finish(out, a, heads: int, kv_heads: int, dv: int, maps: int = 1, difference: float = 0.0, eps: float = 0.0, post: float = 1.0, gate=None, g_off: int = 0) -> None:
+    """What stands between some attentions and their output projection, fp32:
+    ``a`` fp32 [T, heads * maps * dv] holds the attention outputs in the order
+    :func:`qkv_prepare` gave the queries.  ``maps`` 2: ``o = a_1 - difference *
+    a_2``, then ``o / sqrt(mean(o^2) + eps) * post`` per head; ``gate`` (fp32
+    [T, ld], sums of a projection): ``o *= sigmoid(gate[t, g_off + h])``.  out
+    [T, heads * dv] in the compute dtype, heads in their own order."""
+    n = a.shape[0]
+    if tuple(a.shape) != (n, heads * maps * dv) or tuple(out.shape) != (n, heads * dv) or (gate is not None and (gate.shape[0] != n or g_off + heads > gate.shape[1])):
+        raise AlofaError("invalid_argument", "heads_finish sizes disagree", f"a={tuple(a.shape)} out={tuple(out.shape)}")
+    _done(_recurrent().alofa_heads_finish(_dev(out, "out"), _dev(a, "a", torch.float32), _dev(gate, "gate", torch.float32) if gate is not None else None,
+                                          gate.shape[1] if gate is not None else 0, g_off, n, heads, kv_heads, dv, maps, float(difference), float(eps), float(post),
+                                          _is_bf16(out, "out"), _stream()), "heads_finish", f"heads={heads} dv={dv} maps={maps}")
 
 
 def _hyper():
@@ -1060,6 +1108,7 @@ def _hyper():
             "alofa_streams_fill": [_P, _L, _P, _L, _I, _P],
             "alofa_scaled_sum": [_P, _P, _F, _P, _F, _L, _I, _P],
             "alofa_scale_rows": [_P, _F, _L, _P],
+            "alofa_softcap_rows": [_P, _F, _L, _P],
             "alofa_head_gate": [_P, _P, _I, _I, _I, _I, _I, _I, _P],
         }
         for name, args in sigs.items():
@@ -1118,6 +1167,11 @@ def scaled_sum(out, ya, sa: float, yb=None, sb: float = 0.0, accumulate: bool = 
 def scale_rows(x, scale: float) -> None:
     """x *= scale (fp32, in place)."""
     _done(_hyper().alofa_scale_rows(_dev(x, "x", torch.float32), float(scale), x.numel(), _stream()), "scale_rows")
+
+
+def softcap_rows(x, cap: float) -> None:
+    """x = cap * tanh(x / cap) (fp32, in place)."""
+    _done(_hyper().alofa_softcap_rows(_dev(x, "x", torch.float32), float(cap), x.numel(), _stream()), "softcap_rows")
 
 
 def head_gate(o, gate, g_off: int, heads: int, vdim: int) -> None:
@@ -1200,3 +1254,53 @@ def delta_scan(y, v, v_off: int, kn, qn, kq, g, beta, state, q_start, state_slot
     _done(_delta().alofa_delta_scan(_dev(y, "y", f32), _dev(v, "v", f32), v.shape[1], v_off, _dev(kn, "kn", f32), _dev(qn, "qn", f32), _dev(kq, "kq", f32), _dev(g, "g", f32),
                                     _dev(beta, "beta", f32), state.data_ptr(), state.stride(0), _dev(q_start, "q_start", i32), _dev(state_slots, "state_slots", i32),
                                     rows, n_seqs, heads, groups, n, p, spread, _stream()), "delta_scan", f"heads={heads} groups={groups} n={n} p={p}")
+
+
+# -- the real-gated linear recurrent unit ------------------------------------------------------------
+def _gated_lru():
+    lib = _libs.get("gated_lru")
+    if lib is None:
+        lib = load_library("alofa_gated_lru", ["kernels/gated_lru.cu"])
+        sigs = {
+            "alofa_lru_gates": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+            "alofa_lru_scan": [_P, _P, _P, _P, _I, _I, _I, _P, _L, _P, _P, _I, _I, _I, _I, _P],
+        }
+        for name, args in sigs.items():
+            fn = getattr(lib, name)
+            fn.restype = _I
+            fn.argtypes = args
+        _libs["gated_lru"] = lib
+    return lib
+
+
+def lru_gates(a, b, u, wa_t, wi_t, ba, bi, rate, blocks: int) -> None:
+    """Decays and driven inputs of the gated linear recurrent unit, all fp32:
+    per block of ``W / blocks`` channels ``r = sigmoid(A u_b + ba)``, ``i =
+    sigmoid(I u_b + bi)``; ``a = exp(rate * r)`` (``rate`` [W], not positive)
+    and ``b = sqrt(1 - a^2) * i * u``.  u, a, b [T, W]; ``wa_t``, ``wi_t``
+    [blocks, in, out]: the blocks' matrices transposed."""
+    f32 = torch.float32
+    n, width = u.shape
+    if width % blocks:
+        raise AlofaError("invalid_argument", "the blocks must divide the recurrence's width", f"width={width} blocks={blocks}")
+    bs = width // blocks
+    if (tuple(a.shape) != (n, width) or tuple(b.shape) != (n, width) or tuple(wa_t.shape) != (blocks, bs, bs) or tuple(wi_t.shape) != (blocks, bs, bs)
+            or ba.shape[0] != width or bi.shape[0] != width or rate.shape[0] != width):
+        raise AlofaError("invalid_argument", "lru_gates sizes disagree", f"u={tuple(u.shape)} wa={tuple(wa_t.shape)} blocks={blocks}")
+    _done(_gated_lru().alofa_lru_gates(_dev(a, "a", f32), _dev(b, "b", f32), _dev(u, "u", f32), _dev(wa_t, "wa", f32), _dev(wi_t, "wi", f32), _dev(ba, "ba", f32),
+                                       _dev(bi, "bi", f32), _dev(rate, "rate", f32), n, width, blocks, _stream()), "lru_gates", f"width={width} blocks={blocks}")
+
+
+def lru_scan(out, a, b, y, y_off: int, act: str, state, q_start, state_slots, n_seqs: int) -> None:
+    """``S = a_t * S + b_t`` element by element over each request's tokens of
+    the step in order; ``out[t] = S_t * act(y[t, y_off + c])``.  a, b fp32 [T,
+    W]; y fp32 [T, ld]; out [T, W] in its own dtype; state [slots, >= W] fp32,
+    read and left up to date."""
+    n, width = out.shape
+    f32, i32 = torch.float32, torch.int32
+    if tuple(a.shape) != (n, width) or tuple(b.shape) != (n, width) or y.shape[0] != n or y_off + width > y.shape[1]:
+        raise AlofaError("invalid_argument", "lru_scan sizes disagree", f"out={tuple(out.shape)} a={tuple(a.shape)} y={tuple(y.shape)}")
+    _slot_state(state, width, "lru_scan")
+    _done(_gated_lru().alofa_lru_scan(_dev(out, "out"), _dev(a, "a", f32), _dev(b, "b", f32), _dev(y, "y", f32), y.shape[1], y_off, ACTIVATIONS[act], state.data_ptr(),
+                                      state.stride(0), _dev(q_start, "q_start", i32), _dev(state_slots, "state_slots", i32), n_seqs, n, width, _is_bf16(out, "out"),
+                                      _stream()), "lru_scan")

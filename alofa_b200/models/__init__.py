@@ -1,2 +1,2 @@
 """Built-in architectures.  Importing this package registers them."""
-from . import darolix, dibulix, kotutar, qwen2  # noqa: F401
+from . import darolix, dibulix, kikerax, kotutar, qwen2  # noqa: F401

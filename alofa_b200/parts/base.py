@@ -51,12 +51,15 @@ class TensorSpec:
 @dataclass(frozen=True)
 class PagedKV:
     """A mixer's need of a paged key/value cache: ``window`` None = all keys;
-    ``v_head_dim`` None = values as wide as keys."""
+    ``v_head_dim`` None = values as wide as keys; ``v_heads`` None = as many
+    value heads as key heads (fewer where several keys of a head read the
+    same values)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
+    v_heads: Optional[int] = None
 
 
 @dataclass(frozen=True)

@@ -13,6 +13,10 @@ absent).  ``embedding_add``: no sublayers, ``h += e``.
 a weighted sum of them and its output is written back into all of them while
 they are mixed among themselves (see :class:`HyperResidual`).
 
+``postnorm_residual``: a norm on each sublayer's output only, ``h +=
+norm_a(mixer(h)); h += norm_b(feed_forward(h))``; the sublayers read the
+stream itself (the feed-forward may be absent).
+
 ``prenorm_residual``: ``h += mixer(norm_a(h)); h += feed_forward(norm_b(h))``
 (src/alofa/model/arch/qwen.mojo:1367-1372, 1418-1510).  The residual stream
 ``h`` is fp32; the parts add into it."""
@@ -139,6 +143,71 @@ class SandwichResidual(Part):
         x = ctx.buf(tuple(h.shape), self.rt.dtype)
         ops.sandwich_norm(h, y, self.mixer_post.weight, self.mixer_post.eps, x, self.feed_forward_norm.weight, self.feed_forward_norm.eps)
         y = self._sublayer(ctx, self.feed_forward, x, h)
+        ops.sandwich_norm(h, y, self.feed_forward_post.weight, self.feed_forward_post.eps)
+
+
+class PostnormResidual(Part):
+    """A norm on the output of each sublayer, none on its input: the sublayer
+    reads the stream's rows themselves, rounded to the compute dtype.  The
+    sublayer's output goes to an fp32 buffer of its own; one kernel normalises
+    it, adds it to the stream and, for the mixer, also yields the rows the
+    feed-forward reads."""
+
+    family = "block"
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.mixer = build_part("mixer", self.param("mixer"), rt)
+        self.mixer_post = build_part("norm", self.param("mixer_post_norm"), rt)
+        ff = self.params.get("feed_forward")
+        self.feed_forward = build_part("feed_forward", ff, rt) if ff is not None else None
+        self.feed_forward_post = build_part("norm", self.param("feed_forward_post_norm"), rt) if ff is not None else None
+        for part in (self.mixer, self.feed_forward):
+            if part is not None and not getattr(part, "stores_output", False):
+                raise AlofaError("unsupported", "a sublayer whose output is normed must be able to store it", f"kind={part.spec.kind}")
+
+    def parts(self):
+        return tuple(p for p in (self.mixer, self.mixer_post, self.feed_forward, self.feed_forward_post) if p is not None)
+
+    def tensors(self):
+        out = {}
+        for part in self.parts():
+            out.update(part.tensors())
+        return out
+
+    def load(self, state):
+        for part in self.parts():
+            part.load(state)
+
+    @property
+    def graph_safe(self):
+        return all(part.graph_safe for part in self.parts())
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def scratch_row_bytes(self) -> int:
+        return 12 * self.mixer_post.size + sum(getattr(part, "scratch_row_bytes", lambda: 0)() for part in self.parts())
+
+    def forward(self, ctx, h, cache, writes=True):
+        ctx.flush_pending()
+        wide = self.rt.dtype == torch.float32
+        x = h  # the 32-bit path reads the stream in place: a sublayer is done with it before the norm's kernel adds to it
+        if not wide:
+            x = ctx.buf(tuple(h.shape), self.rt.dtype)
+            ops.cast_rows(x, h)
+        y = ctx.buf(tuple(h.shape), torch.float32)
+        self.mixer.forward(ctx, x, y, cache, writes, store=True)
+        if self.feed_forward is None:
+            ops.sandwich_norm(h, y, self.mixer_post.weight, self.mixer_post.eps)
+            return
+        if wide:
+            ops.sandwich_norm(h, y, self.mixer_post.weight, self.mixer_post.eps)
+        else:
+            x = ctx.buf(tuple(h.shape), self.rt.dtype)
+            ops.sandwich_norm(h, y, self.mixer_post.weight, self.mixer_post.eps, x)
+        y = ctx.buf(tuple(h.shape), torch.float32)
+        self.feed_forward.forward(ctx, x, y, store=True)
         ops.sandwich_norm(h, y, self.feed_forward_post.weight, self.feed_forward_post.eps)
 
 
@@ -336,6 +405,7 @@ class HyperResidual(Part):
 
 register_part("block", "hyper_residual", HyperResidual)
 register_part("block", "prenorm_residual", PrenormResidual)
+register_part("block", "postnorm_residual", PostnormResidual)
 register_part("block", "parallel_residual", ParallelResidual)
 register_part("block", "embedding_add", EmbeddingAdd)
 register_part("block", "sandwich_residual", SandwichResidual)

@@ -9,7 +9,8 @@ fp32 product, precise sine and cosine).  The head multiplies the normed
 rows whose logits are wanted by ``lm_head.weight`` if the file has it, else by
 the embedding when the two are tied (qwen.mojo:1077-1089, 1512-1523); a tied
 head shares the embedding's memory.  With ``scale`` the logits are multiplied
-by it."""
+by it; with ``softcap`` they are then bounded by ``softcap * tanh(logits /
+softcap)``."""
 from __future__ import annotations
 
 import torch
@@ -63,6 +64,9 @@ class LinearHead(Part):
         self.tied_to = self.params.get("tied_to")
         self.name = self.prefix + str(self.params.get("weight_name", "weight"))
         self.scale = self.params.get("scale")  # the logits are multiplied by this (None: by nothing)
+        self.softcap = self.params.get("softcap")  # then bounded: softcap * tanh(logits / softcap) (None: not)
+        if self.softcap is not None and not float(self.softcap) > 0:
+            raise AlofaError("invalid_argument", "a head's softcap must be positive", f"softcap={self.softcap}")
         self.linear = None
 
     def tensors(self):
@@ -85,6 +89,8 @@ class LinearHead(Part):
         self.linear(logits, x, buf=ctx.buf)
         if self.scale is not None and float(self.scale) != 1.0:
             ops.scale_rows(logits, float(self.scale))
+        if self.softcap is not None:
+            ops.softcap_rows(logits, float(self.softcap))
         return logits
 
 register_part("embedding", "token_embedding", TokenEmbedding)

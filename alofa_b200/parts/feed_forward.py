@@ -54,7 +54,9 @@ class DenseMLP(Part):
     """``Wdown act(Wup x (+ bup)) (+ bdown)`` with tensors ``<prefix>up``,
     ``<prefix>down`` (``.b`` for the biases); ``activation``: gelu_erf (the
     exact one), gelu_tanh, silu, relu.  The activation is taken on the fp32
-    sums, before they are rounded to the compute dtype."""
+    sums, before they are rounded to the compute dtype.  ``gated``: ``Wdown
+    (silu(Wgate x) * (Wup x))`` with a third tensor ``<prefix>gate``, no
+    biases (gate and up are one product whose epilogue multiplies them)."""
 
     family = "feed_forward"
     graph_safe = True
@@ -66,13 +68,18 @@ class DenseMLP(Part):
         self.inter = int(self.param("intermediate_size"))
         self.act = str(self.param("activation", "gelu_erf"))
         self.bias = bool(self.params.get("bias", False))
+        self.gated = bool(self.params.get("gated", False))
         if self.act not in ops.ACTIVATIONS:
             raise AlofaError("unsupported", "unknown activation", f"activation={self.act} known={sorted(ops.ACTIVATIONS)}")
+        if self.gated and (self.act != "silu" or self.bias):
+            raise AlofaError("unsupported", "a gated feed-forward takes the silu activation and no biases", f"activation={self.act} bias={self.bias}")
         self.up = self.down = None
 
     def tensors(self):
         pre = self.prefix
         t = {pre + "up": TensorSpec((self.inter, self.hidden)), pre + "down": TensorSpec((self.hidden, self.inter))}
+        if self.gated:
+            t[pre + "gate"] = TensorSpec((self.inter, self.hidden))
         if self.bias:
             t[pre + "up.b"] = TensorSpec((self.inter,))
             t[pre + "down.b"] = TensorSpec((self.hidden,))
@@ -80,7 +87,10 @@ class DenseMLP(Part):
 
     def load(self, state):
         pre = self.prefix
-        self.up = Linear(state[pre + "up"], as_float32_vector(state[pre + "up.b"]) if self.bias else None, STORE, act=self.act)
+        if self.gated:  # gate rows first, then up rows
+            self.up = Linear(torch.cat([state[pre + "gate"], state[pre + "up"]], dim=0), None, GATED)
+        else:
+            self.up = Linear(state[pre + "up"], as_float32_vector(state[pre + "up.b"]) if self.bias else None, STORE, act=self.act)
         self.down = Linear(state[pre + "down"], as_float32_vector(state[pre + "down.b"]) if self.bias else None, STORE)
 
     def scratch_row_bytes(self) -> int:

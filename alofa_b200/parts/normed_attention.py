@@ -2,7 +2,9 @@
 options of designs that take positions in by other means:
 
 * ``qk_norm``: q and k are divided by their root mean square over the head's
-  channels (eps inside the root, no weight);
+  channels (eps inside the root); with ``norm_weight`` then multiplied by a
+  plain weight of ``dim`` numbers, one for the queries and one for the keys
+  (``q.norm``, ``k.norm``), shared by all heads;
 * ``q_temp_coef`` / ``q_temp_every``: the query at position p is multiplied by
   ``1 + coef * ln(floor((p + 1) / every) + 1)``;
 * ``scale``: scores are ``(q . k) * scale``;
@@ -12,6 +14,19 @@ options of designs that take positions in by other means:
   fp32 in the kernel) turns the first dimensions of every q and k head;
 * ``sink``: the softmax's denominator holds one more term ``exp(sink)`` that
   belongs to no key and has no value (0.0: "one added to the denominator");
+* ``values`` "keys": there is no value projection, the values are the keys
+  as projected, before their norm;
+* ``gate``: head h's output is multiplied by ``sigmoid(W_g x)_h`` (``g``
+  [heads, hidden]) before the output projection; ``out_bias``: that
+  projection has a bias (``o.b``);
+* ``chunk``: a query at position p sees only the keys from ``p - p % chunk`` on
+  (chunks counted from the sequence's position 0);
+* ``maps`` 2 with ``diff``: differential attention.  Every head has two
+  queries and every key head two keys (rows laid out head by head as [map 1,
+  map 2]), each pair a softmax attention of its own over the same values; with
+  ``lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff`` (tensors of ``dim``
+  numbers) the head's output is ``o = a_1 - lambda a_2``, then ``o /
+  sqrt(mean(o^2) + eps) * (1 - diff)``;
 * keys of ``dim`` channels per head, values of ``vdim`` (the two caches have
   their own widths); query head h reads key/value head ``h // (heads /
   kv_heads)``; causal, all keys or the last ``window``.
@@ -50,6 +65,15 @@ class NormedAttention(PagedAttend, Part):
         self.bias = bool(self.params.get("bias", False))
         self.sink_score = self.params.get("sink")  # None: no sink
         self.sink = None
+        self.norm_weight = bool(self.params.get("norm_weight", False))
+        self.values_from_keys = str(self.params.get("values", "projected")) == "keys"
+        self.gate = bool(self.params.get("gate", False))
+        self.out_bias = bool(self.params.get("out_bias", False))
+        self.chunk = int(self.params.get("chunk") or 0)
+        self.maps = int(self.params.get("maps") or 1)
+        self.diff = float(self.params.get("diff") or 0.0)
+        self.difference = 0.0  # lambda, made at load
+        self.q_weight = self.k_weight = None
         self.position = build_part("position", self.params["position"], rt) if self.params.get("position") is not None else None
         self.rot_dims = int(getattr(self.position, "dims", 0)) if self.position is not None else 0
         if self.position is not None and (not hasattr(self.position, "frequencies") or self.rot_dims > self.dim):
@@ -58,52 +82,100 @@ class NormedAttention(PagedAttend, Part):
             raise AlofaError("invalid_argument", "kv heads must divide heads, sizes must be positive", f"params={self.params}")
         if self.vdim > 256:
             raise AlofaError("unsupported", "value heads of more than 256 channels", f"vdim={self.vdim}")
+        if self.maps not in (1, 2) or (self.maps == 2 and (self.sink_score is not None or self.values_from_keys)):
+            raise AlofaError("unsupported", "one or two softmax maps a head; two take neither a sink nor the keys as values", f"params={self.params}")
+        if self.values_from_keys and self.dim != self.vdim:
+            raise AlofaError("invalid_argument", "keys that are also the values have the values' size", f"dim={self.dim} vdim={self.vdim}")
+        if self.chunk < 0 or (self.chunk and self.window):
+            raise AlofaError("invalid_argument", "a chunked mask takes a positive size and no window beside it", f"chunk={self.chunk} window={self.window}")
+        if self.norm_weight and not self.qk_norm:
+            raise AlofaError("invalid_argument", "a norm's weight needs the norm", f"params={self.params}")
         if self.every <= 0 or self.softcap < 0:
             raise AlofaError("invalid_argument", "q_temp_every must be positive and softcap not negative", f"params={self.params}")
-        self.q_dim, self.k_dim, self.v_dim = self.heads * self.dim, self.kv_heads * self.dim, self.kv_heads * self.vdim
+        self.q_dim, self.k_dim = self.heads * self.maps * self.dim, self.kv_heads * self.maps * self.dim
+        self.v_dim = 0 if self.values_from_keys else self.kv_heads * self.vdim  # columns of the stacked projection
+        self.rows = self.q_dim + self.k_dim + self.v_dim + (self.heads if self.gate else 0)  # [q | k | v | gate]
         self.nh, self.nkv, self.hd = self.heads, self.kv_heads, self.dim  # what the shared choice of kernels goes by (keys and values alike only)
 
     def cache_spec(self):
-        return PagedKV(self.kv_heads, self.dim, self.window, self.vdim)
+        # a chunk never reaches further back than its own size: the pages behind it are given back like a window's
+        return PagedKV(self.kv_heads * self.maps, self.dim, self.chunk or self.window, self.vdim, self.kv_heads)
 
     def scratch_row_bytes(self) -> int:
-        return 4 * (self.q_dim + self.k_dim + self.v_dim) + 4 * self.q_dim + 4 * self.heads * self.vdim + 8 * self.hidden
+        return 4 * self.rows + 4 * self.q_dim + 4 * (self.maps + 1) * self.heads * self.vdim + 8 * self.hidden
 
     def tensors(self):
         pre = self.prefix
-        t = {pre + "q": TensorSpec((self.q_dim, self.hidden)), pre + "k": TensorSpec((self.k_dim, self.hidden)), pre + "v": TensorSpec((self.v_dim, self.hidden)),
-             pre + "o": TensorSpec((self.hidden, self.heads * self.vdim))}
+        t = {pre + "q": TensorSpec((self.q_dim, self.hidden)), pre + "k": TensorSpec((self.k_dim, self.hidden)), pre + "o": TensorSpec((self.hidden, self.heads * self.vdim))}
+        if not self.values_from_keys:
+            t[pre + "v"] = TensorSpec((self.v_dim, self.hidden))
         if self.bias:
-            t.update({pre + "q.b": TensorSpec((self.q_dim,)), pre + "k.b": TensorSpec((self.k_dim,)), pre + "v.b": TensorSpec((self.v_dim,))})
+            t.update({pre + n + ".b": TensorSpec((t[pre + n].shape[0],)) for n in self._stacked()})
+        if self.norm_weight:
+            t.update({pre + "q.norm": TensorSpec((self.dim,), "ones"), pre + "k.norm": TensorSpec((self.dim,), "ones")})
+        if self.gate:
+            t[pre + "g"] = TensorSpec((self.heads, self.hidden))
+        if self.out_bias:
+            t[pre + "o.b"] = TensorSpec((self.hidden,))
+        if self.maps == 2:
+            t.update({pre + n: TensorSpec((self.dim,)) for n in ("lq1", "lk1", "lq2", "lk2")})
         return t
+
+    def _stacked(self):
+        return ("q", "k") if self.values_from_keys else ("q", "k", "v")
 
     def load(self, state):
         pre = self.prefix
-        b = as_float32_vector(torch.cat([state[pre + n + ".b"] for n in "qkv"], dim=0)) if self.bias else None
-        self.qkv = Linear(torch.cat([state[pre + n] for n in "qkv"], dim=0), b, STORE)
+        names = self._stacked()
+        weights = [state[pre + n] for n in names] + ([state[pre + "g"]] if self.gate else [])
+        b = None
+        if self.bias:  # the gate has none
+            b = as_float32_vector(torch.cat([state[pre + n + ".b"] for n in names] + ([torch.zeros_like(state[pre + "q.b"][: self.heads])] if self.gate else []), dim=0))
+        self.qkv = Linear(torch.cat(weights, dim=0), b, STORE)
         if self.position is not None:
             self.position.load(state)
+        dev = state[pre + "o"].device
         if self.sink_score is not None:
-            self.sink = torch.full((self.heads,), float(self.sink_score), dtype=torch.float32, device=state[pre + "o"].device)
-        self.out_add = Linear(state[pre + "o"], None, RESIDUAL)
-        self.out_store = Linear(state[pre + "o"], None, STORE)
+            self.sink = torch.full((self.heads,), float(self.sink_score), dtype=torch.float32, device=dev)
+        if self.norm_weight:
+            self.q_weight, self.k_weight = as_float32_vector(state[pre + "q.norm"]), as_float32_vector(state[pre + "k.norm"])
+        if self.maps == 2:  # one number for the layer, in fp32
+            lq1, lk1, lq2, lk2 = (state[pre + n].to(torch.float32) for n in ("lq1", "lk1", "lq2", "lk2"))
+            self.difference = float((torch.exp((lq1 * lk1).sum()) - torch.exp((lq2 * lk2).sum())).item()) + self.diff
+        ob = as_float32_vector(state[pre + "o.b"]) if self.out_bias else None
+        self.out_add = Linear(state[pre + "o"], ob, RESIDUAL)
+        self.out_store = Linear(state[pre + "o"], ob, STORE)
 
     def forward(self, ctx, x, h, cache, writes=True, store=False):
         if not writes:
             raise AlofaError("unsupported", "this attention does not read another run's cache")
         n, dt = x.shape[0], self.rt.dtype
         group = ctx.groups[cache.group]
-        sums = ctx.buf((n, self.q_dim + self.k_dim + self.v_dim), torch.float32)
+        sums = ctx.buf((n, self.rows), torch.float32)
         self.qkv(sums, x, buf=ctx.buf)
         q = ctx.buf((n, self.q_dim), dt)
+        rotated = self.rot_dims > 0
         ops.qkv_prepare(q, cache.k, cache.v, sums, ctx.positions, group.slot_map, self.heads, self.kv_heads, self.dim, self.vdim, self.qk_norm, self.eps, self.coef, self.every,
-                        self.position.frequencies() if self.rot_dims else None, self.rot_dims)
-        if self.dim == self.vdim:
+                        self.position.frequencies() if rotated else None, self.rot_dims, self.maps, self.q_weight, self.k_weight,
+                        float(getattr(self.position, "magnitude", 1.0)) if rotated else 1.0, self.values_from_keys)
+        g_off = self.q_dim + self.k_dim + self.v_dim  # the gates' column in the stacked projection's sums
+        if self.dim == self.vdim and self.maps == 1 and not self.chunk:
             out = self.attend(ctx, q, cache, group)  # the tensor-core kernels in bfloat16 for the head sizes they are built for, else the every-size kernel
+            if self.gate:
+                if not isinstance(out, torch.Tensor):
+                    out = out.rows()
+                ops.head_gate(out, sums, g_off, self.heads, self.vdim)
         else:
-            out = ctx.buf((n, self.heads * self.vdim), dt)
-            ops.paged_attention_generic(out, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size, self.heads, self.kv_heads,
-                                        self.dim, self.window, self.scale, self.softcap, self.vdim, self.sink)
+            # the every-size kernel; what is still to be combined or gated stays fp32 until it has been
+            plain = self.maps == 1 and not self.gate
+            a = ctx.buf((n, self.heads * self.maps * self.vdim), dt if plain else torch.float32)
+            ops.paged_attention_generic(a, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size, self.heads * self.maps,
+                                        self.kv_heads * self.maps, self.dim, self.window, self.scale, self.softcap, self.vdim, self.sink, self.chunk, self.maps)
+            out = a
+            if not plain:
+                out = ctx.buf((n, self.heads * self.vdim), dt)
+                ops.heads_finish(out, a, self.heads, self.kv_heads, self.vdim, self.maps, self.difference, self.eps, 1.0 - self.diff if self.maps == 2 else 1.0,
+                                 sums if self.gate else None, g_off)
         if store:
             self.out_store(h, out, buf=ctx.buf)
         else:

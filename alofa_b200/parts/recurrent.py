@@ -36,7 +36,16 @@ convolution per channel (no bias) and silu, q and k are made unit vectors per
 head (q also times ``dim^(-1/2)``), ``beta = sigmoid(W_b h)``, ``g =
 exp(-exp(A_log) * softplus(W_a2 (W_a1 h) + dt_bias))``; every head's output is
 RMS-normed over its value channels with one weight shared by the heads and
-multiplied by ``sigmoid(W_g2 (W_g1 h))``, then projected."""
+multiplied by ``sigmoid(W_g2 (W_g1 h))``, then projected.
+
+``gated_lru``: the recurrent block with a real-gated linear recurrent unit.
+Two branches of ``width`` channels: ``y = act(W_y h + b_y)`` and ``u =
+conv(W_x h + b_x)``, a causal convolution per channel with a bias and no
+activation.  The channels form ``blocks`` equal parts, and in each part b ``r =
+sigmoid(A_b u_b + a_b)``, ``i = sigmoid(I_b u_b + i_b)`` with square matrices;
+``log a = -decay_scale * r * softplus(lam)``, ``S_t = a S_(t-1) + sqrt(1 - a^2)
+* i * u`` from ``S = 0`` (the first token is no special case); the output is
+``W_o (S_t * y)``."""
 from __future__ import annotations
 
 import torch
@@ -318,6 +327,70 @@ class GatedDelta(Part):
         _project_out(ctx, self.out_add, self.out_store, h, normed, store)
 
 
+class GatedLRU(Part):
+    family = "mixer"
+    graph_safe = True
+    stores_output = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = self.param
+        self.hidden, self.width, self.blocks, self.taps = int(p("hidden_size")), int(p("width")), int(p("blocks")), int(p("conv"))
+        self.decay_scale = float(p("decay_scale"))
+        self.act = str(p("activation", "gelu_tanh"))
+        if min(self.width, self.blocks, self.taps) <= 0 or self.width % self.blocks or self.decay_scale <= 0:
+            raise AlofaError("invalid_argument", "the recurrent unit's sizes must be positive and blocks must divide its width", f"params={self.params}")
+        if self.act not in ops.ACTIVATIONS:
+            raise AlofaError("unsupported", "unknown activation", f"activation={self.act} known={sorted(ops.ACTIVATIONS)}")
+        self.block_size = self.width // self.blocks
+        if self.block_size > 4096:
+            raise AlofaError("unsupported", "the gates' kernel holds at most 4,096 channels a block", f"width={self.width} blocks={self.blocks}")
+
+    def cache_spec(self):
+        # one fp32 vector per request: the recurrence's state, then the convolution's last inputs
+        return SlotState((self.width * self.taps,), torch.float32)
+
+    def scratch_row_bytes(self) -> int:
+        return 4 * 6 * self.width + 8 * self.hidden
+
+    def tensors(self):
+        pre, w, bs = self.prefix, self.width, self.block_size
+        return {pre + "y": TensorSpec((w, self.hidden)), pre + "y.b": TensorSpec((w,)), pre + "x": TensorSpec((w, self.hidden)), pre + "x.b": TensorSpec((w,)),
+                pre + "conv": TensorSpec((w, self.taps)), pre + "conv.b": TensorSpec((w,)),
+                pre + "ra": TensorSpec((self.blocks, bs, bs)), pre + "ra.b": TensorSpec((self.blocks, bs)),
+                pre + "ri": TensorSpec((self.blocks, bs, bs)), pre + "ri.b": TensorSpec((self.blocks, bs)),
+                pre + "lam": TensorSpec((w,)), pre + "o": TensorSpec((self.hidden, w))}
+
+    def load(self, state):
+        pre, f32 = self.prefix, torch.float32
+        bias = torch.cat([as_float32_vector(state[pre + "y.b"]), as_float32_vector(state[pre + "x.b"])])
+        self.w_in = Linear(torch.cat([state[pre + "y"], state[pre + "x"]], dim=0), bias, STORE)  # [y | x]
+        self.conv_w = state[pre + "conv"].to(f32).contiguous()
+        self.conv_b = as_float32_vector(state[pre + "conv.b"])
+        # the gates are part of the recurrence: fp32 whatever the compute dtype, [block][in][out] for the kernel
+        self.wa_t = state[pre + "ra"].to(f32).transpose(1, 2).contiguous()
+        self.wi_t = state[pre + "ri"].to(f32).transpose(1, 2).contiguous()
+        self.ba = as_float32_vector(state[pre + "ra.b"].reshape(-1))
+        self.bi = as_float32_vector(state[pre + "ri.b"].reshape(-1))
+        self.rate = (-self.decay_scale * torch.nn.functional.softplus(state[pre + "lam"].to(f32))).contiguous()  # log a = rate * r
+        self.out_add = Linear(state[pre + "o"], None, RESIDUAL)
+        self.out_store = Linear(state[pre + "o"], None, STORE)
+
+    def forward(self, ctx, x, h, cache, writes=True, store=False):
+        n, w, f32 = x.shape[0], self.width, torch.float32
+        u = ctx.buf((n, 2 * w), f32)  # the projections' fp32 sums, biases added
+        self.w_in(u, x, buf=ctx.buf)
+        st = cache.state
+        xc = ctx.buf((n, w), f32)
+        ops.causal_conv(xc, u, w, self.conv_w, self.conv_b, st[:, w:], ctx.q_start, ctx.state_slots, ctx.seq_of_token, ctx.n_seqs, act=False)
+        a, b = ctx.buf((n, w), f32), ctx.buf((n, w), f32)
+        ops.lru_gates(a, b, xc, self.wa_t, self.wi_t, self.ba, self.bi, self.rate, self.blocks)
+        y = ctx.buf((n, w), self.rt.dtype)
+        ops.lru_scan(y, a, b, u, 0, self.act, st, ctx.q_start, ctx.state_slots, ctx.n_seqs)
+        _project_out(ctx, self.out_add, self.out_store, h, y, store)
+
+
+register_part("mixer", "gated_lru", GatedLRU)
 register_part("mixer", "min_gru", MinGRU)
 register_part("mixer", "gated_delta", GatedDelta)
 register_part("mixer", "state_space", StateSpaceMixer)

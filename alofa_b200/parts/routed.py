@@ -10,7 +10,11 @@ input (``weight_on_input``) or its output.  Options: ``gated`` experts
 stored vector added to the scores for the choice only (the weights stay the
 scores); ``identity``: the last so many of the router's outputs are experts
 without tensors whose output is their input; ``renorm_eps`` added to the sum
-that ``renormalize`` divides by.  A shared expert of the same form
+that ``renormalize`` divides by; ``groups`` / ``keep``: the experts form
+``groups`` equal groups of neighbours, a group's score is the sum of its two
+largest choice scores (score + correction), and only experts of the ``keep``
+best groups can be chosen; ``route_scale``: a factor on the weights.  A shared
+expert of the same form
 (``shared_ff`` > 0) runs for every token and is added, times ``sigmoid(x
 wsg^T)`` when ``shared_gate`` is set.
 
@@ -53,6 +57,12 @@ class RoutedExperts(Part):
         self.identity = int(self.params.get("identity") or 0)
         self.correction_name = self.prefix + "correction" if self.params.get("correction") else None
         self.renorm_eps = float(self.params.get("renorm_eps") or 0.0)
+        self.groups = int(self.params.get("groups") or 1)
+        self.keep = int(self.params.get("keep") or self.groups)
+        self.route_scale = float(self.params.get("route_scale", 1.0))
+        if self.groups > 1 and (self.identity or self.experts % self.groups or not 0 < self.keep <= self.groups or self.keep * (self.experts // self.groups) < self.top):
+            raise AlofaError("invalid_argument", "groups must divide the experts, and the groups kept must hold at least top experts",
+                             f"experts={self.experts} groups={self.groups} keep={self.keep} top={self.top}")
         self.routed = self.experts + self.identity  # outputs of the router
         if self.gated and self.act != "silu":
             raise AlofaError("unsupported", "gated experts take the silu activation only", f"activation={self.act}")
@@ -66,7 +76,7 @@ class RoutedExperts(Part):
         if self.shared_ff:
             from ..config.spec import PartSpec
 
-            self.shared = DenseMLP(PartSpec("mlp", {"hidden_size": self.hidden, "intermediate_size": self.shared_ff, "activation": self.act, "bias": False},
+            self.shared = DenseMLP(PartSpec("mlp", {"hidden_size": self.hidden, "intermediate_size": self.shared_ff, "activation": self.act, "bias": False, "gated": self.gated},
                                             prefix=self.prefix + "shared."), rt)
 
     def tensors(self):
@@ -108,7 +118,8 @@ class RoutedExperts(Part):
         i32, f32 = torch.int32, torch.float32
         choice, weight = ctx.buf((n, top), i32), ctx.buf((n, top), f32)
         gate = ctx.buf((n,), f32) if self.shared_gate else None
-        ops.moe_router(choice, weight, gate, x, self.router, self.routed, top, self.score == "softmax", self.renormalize, self.correction, self.renorm_eps)
+        ops.moe_router(choice, weight, gate, x, self.router, self.routed, top, self.score == "softmax", self.renormalize, self.correction, self.renorm_eps,
+                       self.groups, self.keep, self.route_scale)
         pairs = n * top
         tiles = -(-pairs // tile) + self.experts  # every expert may end on a tile that is not full
         dest, tile_expert = ctx.buf((n, top), i32), ctx.buf((tiles,), i32)
