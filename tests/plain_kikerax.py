@@ -34,7 +34,7 @@ def load(folder):
 
 
 def sigmoid(z):
-    return 1.0 / (1.0 + np.exp(-z))
+    return 0.5 * (1.0 + np.tanh(0.5 * np.asarray(z, dtype=np.float64)))
 
 
 def silu(z):

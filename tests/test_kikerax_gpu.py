@@ -1,0 +1,600 @@
+"""Kikerax on the GPU against the plain implementation (tests/plain_kikerax.py).
+
+Mechanisms alone (kernels against the plain function of the same mechanism):
+differential attention in chunks over paged keys (two maps a head over one
+value head, weighted norms, a rotated part of each map with stretched
+frequencies, lengths around page and chunk borders, in prompts, portions and
+decoding; one key made to stand out just inside and just outside a chunk), the
+attention whose values are its keys (temperature, cap, a far key among
+hundreds), the recurrent unit over portions and reused slots (a far token whose
+trace must survive), the router among the best groups, the norm on a
+sublayer's output, the gated feed-forward, the logit cap.  Then whole models of
+four configurations, in 32-bit and bfloat16: whole prompts, prefill against
+token-by-token decoding, portions down to two tokens, batches of unequal
+requests in a pool so small that pages and slots are used again, long decoding
+from the first token, the stream after every layer, and greedy generation
+through the engine and the programs."""
+import json
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_kikerax as plain
+import replay
+import tiny_kikerax as tiny
+from gpu_util import assert_close, dev, rounded
+
+pytestmark = pytest.mark.gpu
+
+F32, BF16 = torch.float32, torch.bfloat16
+# Largest |engine - plain| on logits, times max(1, max|plain|): fp32 sums against float64; bfloat16 rounds
+# activations and cache rows to 8 bits of mantissa.
+TOL = {"float32": 3e-5, "bfloat16": 9e-2}
+KERNEL_TOL = {F32: 2e-5, BF16: 3e-2}
+
+
+def meta(counts, slots):
+    q_start = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    seq = np.concatenate([np.full(c, s, dtype=np.int32) for s, c in enumerate(counts)])
+    return dev(q_start), dev(np.asarray(slots, dtype=np.int32)), dev(seq)
+
+
+# ---------------------------------------------------------------------------------------------------
+# attention: the kernels' pipeline (prepare, attend, finish) against the plain mixer with weights that
+# pick q, k, v and the gates' logits out of the input, so that a test can make them what it wants
+# ---------------------------------------------------------------------------------------------------
+def picking_weights(rng, m, maps, prefix="a."):
+    """The input is [q | k | v | gate logits]; the projections pick their columns; the output projection is the identity."""
+    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    nq, nk, nv = H * maps * d, G * maps * d, 0 if maps == 1 else G * dv
+    width = nq + nk + nv + H
+    eye = np.eye(width)
+    w = {"q": eye[:nq], "k": eye[nq : nq + nk], "g": eye[nq + nk + nv :], "o": np.eye(H * dv), "q.norm": rounded(1 + 0.3 * rng.standard_normal(d), F32),
+         "k.norm": rounded(1 + 0.3 * rng.standard_normal(d), F32)}
+    if maps == 2:
+        w.update({"v": eye[nq + nk : nq + nk + nv], "q.b": np.zeros(nq), "k.b": np.zeros(nk), "v.b": np.zeros(nv), "o.b": np.zeros(H * dv)})
+        w.update({n: rounded(rng.standard_normal(d) / np.sqrt(np.sqrt(d)), F32) for n in ("lq1", "lk1", "lq2", "lk2")})
+    return {prefix + n: v for n, v in w.items()}, width
+
+
+class PagedCase:
+    """Requests of given lengths over one paged cache with block tables in random order."""
+
+    def __init__(self, rng, lengths, page, k_heads, d, v_heads, dv, dtype):
+        self.page, self.lengths = page, lengths
+        blocks = [-(-n // page) for n in lengths]
+        order = rng.permutation(sum(blocks) + 3)
+        self.table = np.full((len(lengths), max(blocks) + 1), -1, dtype=np.int32)
+        at = 0
+        for r, b in enumerate(blocks):
+            self.table[r, :b] = order[at : at + b]
+            at += b
+        slots = (sum(blocks) + 3) * page
+        self.k = torch.full((slots, k_heads, d), 7.0, dtype=dtype, device="cuda")  # what lies in unused slots must not matter
+        self.v = torch.full((slots, v_heads, dv), -7.0, dtype=dtype, device="cuda")
+        self.table_dev = dev(self.table)
+
+    def slot_map(self, r, lo, hi):
+        return np.array([self.table[r, j // self.page] * self.page + j % self.page for j in range(lo, hi)], dtype=np.int32)
+
+
+def attend(case, m, maps, w, rows, spans, dtype, eps, prefix="a."):
+    """The kernels' pipeline over the rows ``spans`` = [(request, lo, hi)] of ``rows[request]`` in one step."""
+    from alofa_b200.csrc import ops
+
+    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    sums = np.concatenate([rows[r][lo:hi] for r, lo, hi in spans])
+    n = sums.shape[0]
+    positions = dev(np.concatenate([np.arange(lo, hi, dtype=np.int32) for _, lo, hi in spans]))
+    seq = dev(np.concatenate([np.full(hi - lo, r, dtype=np.int32) for r, lo, hi in spans]))
+    slot_map = dev(np.concatenate([case.slot_map(r, lo, hi) for r, lo, hi in spans]))
+    q = torch.empty((n, H * maps * d), dtype=dtype, device="cuda")
+    rot = m.get("rot")
+    freq, mag = plain.rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling")) if rot else (None, 1.0)
+    temp = m.get("q_temp") or {"coef": 0.0, "every": 1}
+    ops.qkv_prepare(q, case.k, case.v, dev(sums, F32), positions, slot_map, H, G, d, dv, True, eps, temp["coef"], temp["every"],
+                    dev(freq.astype(np.float32)) if rot else None, rot["dims"] if rot else 0, maps, dev(w[prefix + "q.norm"], F32), dev(w[prefix + "k.norm"], F32), mag, maps == 1)
+    a = torch.empty((n, H * maps * dv), dtype=F32, device="cuda")
+    ops.paged_attention_generic(a, q, case.k, case.v, positions, seq, case.table_dev, case.page, H * maps, G * maps, d, None, m["scale"], m.get("softcap") or 0.0, dv, None,
+                                (m.get("mask") or {}).get("size", 0), maps)
+    out = torch.empty((n, H * dv), dtype=dtype, device="cuda")
+    lam = plain.difference_weight(w, prefix, m["diff"]) if maps == 2 else 0.0
+    ops.heads_finish(out, a, H, G, dv, maps, lam, eps, 1.0 - m["diff"] if maps == 2 else 1.0, dev(sums, F32), sums.shape[1] - H)
+    return out.float().cpu().numpy()
+
+
+def in_steps(case, m, maps, w, rows, dtype, eps, cuts):
+    """Every request whole in one step; then again from an empty cache in portions of ``cuts`` (1: decoding) with all requests in every step."""
+    whole = attend(case, m, maps, w, rows, [(r, 0, n) for r, n in enumerate(case.lengths)], dtype, eps)
+    split = np.cumsum([0] + list(case.lengths))
+    out = [[whole[split[r] : split[r + 1]] for r in range(len(rows))]]
+    case.k.fill_(7.0)
+    case.v.fill_(-7.0)
+    got, at, step = [[] for _ in rows], [0] * len(rows), 0
+    while any(at[r] < n for r, n in enumerate(case.lengths)):
+        spans = []
+        for r, n in enumerate(case.lengths):
+            if at[r] < n:
+                c = min(cuts[(step + r) % len(cuts)], n - at[r])
+                spans.append((r, at[r], at[r] + c))
+        step += 1
+        res, k = attend(case, m, maps, w, rows, spans, dtype, eps), 0
+        for r, lo, hi in spans:
+            got[r].append(res[k : k + hi - lo])
+            k += hi - lo
+            at[r] = hi
+    out.append([np.concatenate(g) for g in got])
+    return out
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("H,G,d,dv,chunk,rot", [(4, 2, 16, 24, 9, (300.0, 8, (4.0, 64, 8.0, 1.0))), (3, 3, 12, 8, 21, (100.0, 12, None)), (2, 1, 10, 30, None, None),
+                                               (1, 1, 8, 12, 2, (7.0, 8, (2.0, 16, 4.0, 0.5))), (6, 2, 40, 72, 32, (20000.0, 10, (3.0, 128, 16.0, 2.0))), (2, 2, 64, 64, 16, (1000.0, 64, None))])
+def test_differential_attention_in_chunks_over_paged_keys(dtype, H, G, d, dv, chunk, rot):
+    """Two maps a head over one value head, weighted norms, part of each map turned, chunks counted from the sequence's
+    start: whole prompts, portions that end inside chunks and pages, and decoding, at lengths around page (16) and
+    chunk borders."""
+    rng = np.random.default_rng(3)
+    m = {"heads": H, "kv_heads": G, "dim": d, "vdim": dv, "scale": 2.0 / np.sqrt(d), "diff": 0.35}
+    if chunk:
+        m["mask"] = {"size": chunk}
+    if rot:
+        m["rot"] = {"base": rot[0], "dims": rot[1], "scaling": dict(zip(("factor", "original", "fast", "slow"), rot[2])) if rot[2] else None}
+    w, width = picking_weights(rng, m, 2)
+    edges = sorted({1, 2, 15, 16, 17, 33, 70} | ({chunk - 1, chunk, chunk + 1, 2 * chunk, 2 * chunk + 1, 3 * chunk - 1} if chunk and chunk > 2 else set()))
+    lengths = [n for n in edges if n > 0]
+    rows = [rounded(rng.standard_normal((n, width)), F32) for n in lengths]
+    eps = 1e-5
+    want = [plain.differential_attention(w, "a.", m, x, eps) for x in rows]
+    for cuts in ((1,), (5, 2, 16, 3, 2, 33)):
+        case = PagedCase(rng, lengths, 16, 2 * G, d, G, dv, dtype)
+        for what, got in zip(("whole", f"portions of {cuts}"), in_steps(case, m, 2, w, rows, dtype, eps, cuts)):
+            for r, n in enumerate(lengths):
+                assert_close(got[r], want[r], KERNEL_TOL[dtype], f"{what}: request of {n} tokens")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("chunk", [3, 16, 40, 100])
+def test_a_key_just_inside_and_just_outside_a_chunk(dtype, chunk):
+    """The query at a chunk's last position and the one at the next chunk's first both point the way of the chunk's
+    FIRST key (map 1) and of the key before it, whose values are large: the first query must take the first key's
+    value and not the one before, the second query neither.  In a prompt and in decoding."""
+    rng = np.random.default_rng(4)
+    H, G, d, dv, eps = 2, 1, 16, 8, 1e-6
+    m = {"heads": H, "kv_heads": G, "dim": d, "vdim": dv, "scale": 1.0, "diff": 0.2, "mask": {"size": chunk}}
+    w, width = picking_weights(rng, m, 2)
+    for n in ("q.norm", "k.norm"):
+        w["a." + n] = np.ones(d)
+    n = 3 * chunk + 2
+    x = rounded(rng.standard_normal((n, width)), F32)
+    start = 2 * chunk  # the third chunk's first position
+    way = rng.standard_normal(d)
+    kcol, vcol = H * 2 * d, H * 2 * d + G * 2 * d
+    x[start, kcol : kcol + d] = way  # map 1 of the key at the chunk's start
+    x[start - 1, kcol : kcol + d] = way  # and of the key just before the chunk
+    x[start, vcol : vcol + dv] = 40.0
+    x[start - 1, vcol : vcol + dv] = -40.0
+    for i in (start + chunk - 1, start + chunk, start - 1):  # the chunk's last query, the next chunk's first, the chunk before's last
+        x[i, :d] = way
+        x[i, 2 * d : 3 * d] = way
+    x = rounded(x, F32)
+    want = plain.differential_attention(w, "a.", m, x, eps)
+    inside, outside = want[start + chunk - 1], want[start + chunk]
+    assert np.abs(inside - outside).max() > 0.3, "the test's keys do not stand out"
+    for cuts in ((1,), (7, 2, 64)):
+        case = PagedCase(rng, [n], 16, 2 * G, d, G, dv, dtype)
+        for got in in_steps(case, m, 2, w, [x], dtype, eps, cuts):
+            assert_close(got[0], want, KERNEL_TOL[dtype], f"chunk {chunk}, cuts {cuts}")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("H,G,d,softcap,temp", [(6, 3, 16, 5.0, (0.4, 7)), (5, 5, 12, None, None), (4, 2, 64, 20.0, (0.5, 16)), (4, 1, 8, 50.0, (0.7, 50)), (2, 2, 40, None, (1.0, 3))])
+def test_attention_whose_values_are_its_keys(dtype, H, G, d, softcap, temp):
+    """Weighted norms of q and k, the keys as projected for values, queries that grow with the position, capped scores,
+    a gate per head; every key visible: prompts, portions and decoding at lengths around page borders."""
+    rng = np.random.default_rng(5)
+    m = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": 2.0 / np.sqrt(d)}
+    if softcap:
+        m["softcap"] = softcap
+    if temp:
+        m["q_temp"] = {"coef": temp[0], "every": temp[1]}
+    w, width = picking_weights(rng, m, 1)
+    lengths = [1, 2, 15, 16, 17, 127, 128, 129, 200]
+    rows = [rounded(rng.standard_normal((n, width)) * 1.5, F32) for n in lengths]
+    eps = 1e-5
+    want = [plain.keyed_attention(w, "a.", m, x, eps) for x in rows]
+    for cuts in ((1,), (5, 2, 16, 3, 2, 33)):
+        case = PagedCase(rng, lengths, 16, G, d, G, d, dtype)
+        for what, got in zip(("whole", f"portions of {cuts}"), in_steps(case, m, 1, w, rows, dtype, eps, cuts)):
+            for r, n in enumerate(lengths):
+                assert_close(got[r], want[r], KERNEL_TOL[dtype], f"{what}: request of {n} tokens")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_one_far_key_among_hundreds(dtype):
+    """Key 3 of 700 and the last query point the same way: after norm, scale and cap that key holds most of the
+    weight; the output must be (nearly) its value, which a lost page or a wrong position would not give."""
+    rng = np.random.default_rng(6)
+    H, G, d, eps = 2, 1, 32, 1e-6
+    m = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": 0.5, "softcap": 14.0}
+    w, width = picking_weights(rng, m, 1)
+    for n in ("q.norm", "k.norm"):
+        w["a." + n] = np.ones(d)
+    x = rounded(rng.standard_normal((700, width)), F32)
+    way = rng.standard_normal(d)
+    x[3, H * d : H * d + d] = 6.0 * way
+    x[699, :d] = way
+    x[:, -H:] = 30.0  # the gates wide open
+    want = plain.keyed_attention(w, "a.", m, x, eps)
+    assert np.abs(want[699, :d] - x[3, H * d : H * d + d]).max() < 0.2 * np.abs(x[3, H * d : H * d + d]).max(), "the test's far key does not stand out"
+    case = PagedCase(rng, [700], 16, G, d, G, d, dtype)
+    attend(case, m, 1, w, [x], [(0, 0, 699)], dtype, eps)
+    got = attend(case, m, 1, w, [x], [(0, 699, 700)], dtype, eps)
+    assert_close(got, want[699:], KERNEL_TOL[dtype] * 12, "last query")  # values as large as 12
+
+
+# ---------------------------------------------------------------------------------------------------
+# the recurrent unit
+# ---------------------------------------------------------------------------------------------------
+def unit_weights(rng, W, B, K, slow=False):
+    bs = W // B
+    w = {"y": np.eye(2 * W)[:W], "y.b": rng.standard_normal(W) * 0.3, "x": np.eye(2 * W)[W:], "x.b": rng.standard_normal(W) * 0.3,
+         "conv": rng.standard_normal((W, K)) / np.sqrt(K) + (np.arange(K) == K - 1), "conv.b": rng.standard_normal(W) * 0.3,
+         "ra": 2 * rng.standard_normal((B, bs, bs)) / np.sqrt(bs), "ra.b": rng.standard_normal((B, bs)) * 0.5, "ri": 2 * rng.standard_normal((B, bs, bs)) / np.sqrt(bs),
+         "ri.b": rng.standard_normal((B, bs)) * 0.5, "lam": rng.uniform(-12.0, -9.0, W) if slow else rng.uniform(-6.0, -1.0, W), "o": np.eye(W)}
+    return {"r." + n: rounded(v, F32) for n, v in w.items()}
+
+
+class Unit:
+    """The kernels of the recurrent unit with a state per slot, as the part runs them."""
+
+    def __init__(self, w, W, B, K, slots, dtype):
+        self.W, self.B, self.K, self.dtype = W, B, K, dtype
+        self.state = torch.zeros((slots, W * K), dtype=F32, device="cuda")
+        self.bias = np.concatenate([w["r.y.b"], w["r.x.b"]])
+        self.conv_w, self.conv_b = dev(w["r.conv"], F32), dev(w["r.conv.b"], F32)
+        self.wa, self.wi = dev(np.transpose(w["r.ra"], (0, 2, 1)), F32), dev(np.transpose(w["r.ri"], (0, 2, 1)), F32)
+        self.ba, self.bi = dev(w["r.ra.b"].reshape(-1), F32), dev(w["r.ri.b"].reshape(-1), F32)
+        self.rate = dev(-8.0 * np.log1p(np.exp(w["r.lam"])), F32)
+
+    def step(self, x, q_start, slots, seq, n_seqs):
+        from alofa_b200.csrc import ops
+
+        n, W = x.shape[0], self.W
+        u = dev(x + self.bias, F32)
+        xc = torch.empty((n, W), dtype=F32, device="cuda")
+        ops.causal_conv(xc, u, W, self.conv_w, self.conv_b, self.state[:, W:], q_start, slots, seq, n_seqs, act=False)
+        a, b = torch.empty_like(xc), torch.empty_like(xc)
+        ops.lru_gates(a, b, xc, self.wa, self.wi, self.ba, self.bi, self.rate, self.B)
+        y = torch.empty((n, W), dtype=self.dtype, device="cuda")
+        ops.lru_scan(y, a, b, u, 0, "gelu_tanh", self.state, q_start, slots, n_seqs)
+        return y.float().cpu().numpy()
+
+
+def in_portions(lengths, cuts, slots_of, run):
+    """Walk requests of ``lengths`` tokens through steps: request r brings ``cuts[(step + r) % len(cuts)]`` tokens and
+    sits out every third step.  ``run(spans, q_start, slots, seq)`` -> rows of the step; returns every request's rows in order."""
+    got = [[] for _ in lengths]
+    at = [0] * len(lengths)
+    step = 0
+    while any(at[r] < lengths[r] for r in range(len(lengths))):
+        live = [r for r in range(len(lengths)) if at[r] < lengths[r] and (step + r) % 3 != 2]
+        step += 1
+        if not live:
+            continue
+        counts = [min(cuts[(step + r) % len(cuts)], lengths[r] - at[r]) for r in live]
+        spans = [(r, at[r], at[r] + c) for r, c in zip(live, counts)]
+        q_start, slots, seq = meta(counts, [slots_of[r] for r in live])
+        rows = run(spans, q_start, slots, seq)
+        k = 0
+        for r, c in zip(live, counts):
+            got[r].append(rows[k : k + c])
+            k += c
+            at[r] += c
+    return [np.concatenate(g) for g in got]
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("W,B,K", [(48, 3, 3), (70, 1, 1), (128, 2, 4), (40, 40, 2), (600, 2, 4)])
+def test_recurrent_unit_over_portions_in_slots_used_out_of_order(dtype, W, B, K):
+    """Convolution, gates and recurrence carried from step to step: portions of 1, 2 and many tokens (long enough for
+    sixteen stretches), requests that sit steps out, slots in another order than the requests."""
+    rng = np.random.default_rng(7)
+    w = unit_weights(rng, W, B, K)
+    m = {"width": W, "blocks": B, "conv": K}
+    lengths = [1, 2, 37, 150, 700]
+    xs = [rounded(rng.standard_normal((n, 2 * W)), F32) for n in lengths]
+    want = [plain.gated_recurrent_unit(w, "r.", m, x) for x in xs]
+    unit = Unit(w, W, B, K, 7, dtype)
+    unit.state.fill_(3.0)  # what a slot's last user left
+    slots_of = [5, 0, 3, 6, 1]
+    for s in slots_of:
+        unit.state[s].zero_()  # as the engine does when a request is admitted
+    for cuts in ((1, 2, 3, 17, 600), (1,)):
+        if cuts == (1,):
+            lengths_now, xs_now, want_now, slots_now = lengths[:4], xs[:4], want[:4], [2, 4, 5, 0]
+            for s in slots_now:
+                unit.state[s].zero_()
+        else:
+            lengths_now, xs_now, want_now, slots_now = lengths, xs, want, slots_of
+        got = in_portions(lengths_now, cuts, slots_now, lambda spans, q_start, slots, seq: unit.step(np.concatenate([xs_now[r][lo:hi] for r, lo, hi in spans]), q_start, slots, seq, len(spans)))
+        for r, n in enumerate(lengths_now):
+            assert_close(got[r], want_now[r], KERNEL_TOL[dtype], f"cuts {cuts}: request of {n} tokens")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_a_far_token_is_read_back_from_the_state(dtype):
+    """Token 2 of 400 is large and the decays are near one: 390 tokens later most of the state is still its trace,
+    which a state lost at a step's border or a slot mixed up would not show."""
+    rng = np.random.default_rng(8)
+    W, B, K = 32, 2, 2
+    w = unit_weights(rng, W, B, K, slow=True)
+    m = {"width": W, "blocks": B, "conv": K}
+    x = rounded(rng.standard_normal((400, 2 * W)) * 0.2, F32)
+    x[2, W:] = 200.0
+    x[:, :W] = 2.0  # the other branch: the same factor everywhere
+    want = plain.gated_recurrent_unit(w, "r.", m, x)
+    quiet = x.copy()
+    quiet[2, W:] = 0.0
+    assert np.abs(want[395] - plain.gated_recurrent_unit(w, "r.", m, quiet)[395]).max() > 1.0, "the test's far token leaves no trace"
+    unit = Unit(w, W, B, K, 3, dtype)
+    got = in_portions([400], (3, 1, 150, 1, 1, 2, 90), [1], lambda spans, q_start, slots, seq: unit.step(np.concatenate([x[lo:hi] for _, lo, hi in spans]), q_start, slots, seq, 1))
+    assert_close(got[0], want, KERNEL_TOL[dtype], "every token")
+
+
+# ---------------------------------------------------------------------------------------------------
+# router, norms, feed-forward, head
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("experts,top,groups,keep,scale", [(6, 2, 3, 2, 1.5), (12, 4, 4, 3, 2.0), (4, 1, 4, 2, 2.5), (9, 3, 3, 1, 1.0), (8, 2, 1, 1, 0.5), (64, 6, 8, 4, 2.5), (40, 5, 40, 7, 1.0)])
+def test_router_among_the_best_groups(experts, top, groups, keep, scale):
+    """Choices by score + correction among the experts of the kept groups only (a group's score: its two largest choice
+    scores), weights from the scores alone over their sum, times the scale."""
+    from alofa_b200.csrc import ops
+
+    rng = np.random.default_rng(11)
+    n, hidden = 97, 48
+    x = rounded(rng.standard_normal((n, hidden)), F32)
+    w = {"m.router": rounded(2 * rng.standard_normal((experts, hidden)) / np.sqrt(hidden), F32), "m.correction": rounded(0.3 * rng.standard_normal(experts) - 0.4, F32)}
+    r = {"experts": experts, "top": top, "scale": scale}
+    if groups > 1:
+        r["groups"] = {"count": groups, "keep": keep}
+    chosen, weight, margin = plain.route(w, "m.", r, x)
+    if 1 < groups and keep < groups and experts > groups:  # groups of one expert always hold the best experts
+        free, _, _ = plain.route(w, "m.", {"experts": experts, "top": top, "scale": scale}, x)
+        assert (np.sort(chosen, 1) != np.sort(free, 1)).any(), "the test's groups change no choice"
+    choice = torch.empty((n, top), dtype=torch.int32, device="cuda")
+    wgt = torch.empty((n, top), dtype=F32, device="cuda")
+    ops.moe_router(choice, wgt, None, dev(x, F32), dev(w["m.router"], F32), experts, top, False, True, dev(w["m.correction"], F32), 1e-20, groups, keep, scale)
+    sure = margin > 1e-5
+    assert sure.mean() > 0.9
+    assert (choice.cpu().numpy()[sure] == chosen[sure]).all()
+    assert_close(wgt.cpu().numpy()[sure], weight[sure], 1e-5, "weights")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("width", [96, 100, 1030, 2560])
+def test_norm_on_a_sublayers_output_and_the_rows_the_next_one_reads(dtype, width):
+    from alofa_b200.csrc import ops
+
+    rng = np.random.default_rng(12)
+    n, eps = 9, 3e-6
+    h, y, wgt = (rounded(rng.standard_normal(s) * 2, F32) for s in ((n, width), (n, width), (width,)))
+    hd, x = dev(h, F32), torch.empty((n, width), dtype=dtype, device="cuda")
+    ops.sandwich_norm(hd, dev(y, F32), dev(wgt, F32), eps, x)
+    want = h + plain.rms_norm(y, wgt, eps)
+    assert_close(hd.cpu(), want, 1e-6, "stream")
+    assert_close(x.float().cpu(), rounded(hd.cpu().numpy(), dtype), 0, "the rows themselves, rounded once")
+    z = torch.empty((n, width), dtype=dtype, device="cuda")
+    ops.cast_rows(z, hd)
+    assert torch.equal(z, x)
+
+
+@pytest.mark.parametrize("cap", [0.5, 8.0, 30.0])
+def test_logit_cap(cap):
+    from alofa_b200.csrc import ops
+
+    x = np.linspace(-80, 80, 1001).reshape(7, 143).astype(np.float32)
+    t = dev(x, F32)
+    ops.softcap_rows(t, cap)
+    assert_close(t.cpu(), cap * np.tanh(x.astype(np.float64) / cap), 1e-6, "capped")
+
+
+# ---------------------------------------------------------------------------------------------------
+# whole models
+# ---------------------------------------------------------------------------------------------------
+LENGTHS = {"A": [1, 2, 23, 64, 65, 129, 200], "B": [3, 16, 17, 33, 80, 131], "C": [5, 64, 190, 257], "D": [2, 63, 150, 300]}
+DECODED = 12
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = tmp_path_factory.mktemp("kikerax_gpu")
+    return {name: tiny.write(base / name, name, seed=10 + i) for i, name in enumerate(tiny.CONFIGS)}
+
+
+def make_requests(name):
+    reqs, prompts = {}, {}
+    for i, n in enumerate(LENGTHS[name]):
+        reqs[f"r{i}"] = tiny.tokens(name, n + DECODED, seed=i)
+        prompts[f"r{i}"] = n
+    return reqs, prompts
+
+
+@pytest.fixture(scope="module")
+def plain_logits(folders):
+    out = {}
+    for name, folder in folders.items():
+        w, cfg = plain.load(folder)
+        logits, sure = {}, {}
+        for rid, toks in make_requests(name)[0].items():
+            logits[rid] = plain.forward(w, cfg, toks)
+            sure[rid] = plain.sure_prefix(plain.router_margins(w, cfg, toks))
+        out[name] = (logits, sure)
+    return out
+
+
+def runner_for(folder, dtype, block, pages, max_requests=4, graphs=True):
+    from alofa_b200.engine.loading import load_model
+    from alofa_b200.engine.step import StepRunner
+
+    model, *_ = load_model(folder, dtype)
+    return StepRunner(model, block_size=block, num_pages=pages, max_requests=max_requests, max_tokens=pages * block, max_step_tokens=512, cuda_graphs=graphs)
+
+
+def assert_most_close(errors, tol, what):
+    errors = np.asarray(errors)
+    assert (errors > tol).mean() <= 0.25 and np.median(errors) <= tol / 3, \
+        f"{what}: {(errors > tol).sum()} of {len(errors)} positions beyond {tol:.1e}, median {np.median(errors):.3e}, worst {errors.max():.3e}"
+
+
+def compare(steps, outputs, want, vocab, tol, what, sure=None):
+    """Every position within ``tol`` in 32-bit.  In bfloat16 strictly up to a request's first close call of a router
+    (``sure``): a routed feed-forward is not continuous, and where two choice scores lie within rounding bfloat16 may
+    rightly take the other expert; that position, and through state and cache the ones after it, then differ by more
+    than rounding.  Over all positions three quarters keep the bound and the median a third of it: a lost state, a
+    wrong key or page moves every position by order one."""
+    got = replay.collect(steps, outputs, vocab)
+    errors = []
+    for rid, rows in got.items():
+        ref = want[rid][: len(rows)]
+        assert rows.shape == ref.shape, f"{what} {rid}: {rows.shape} vs {ref.shape}"
+        err = np.abs(rows - ref).max(axis=-1) / max(1.0, float(np.abs(ref).max()))
+        n = len(rows) if sure is None else min(len(rows), sure[rid])
+        if n:
+            assert err[:n].max() <= tol, f"{what} {rid}: position {int(err[:n].argmax())} differs by {err[:n].max():.3e} > {tol:.1e}"
+        errors.append(err)
+    assert_most_close(np.concatenate(errors), tol, what)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(tiny.CONFIGS))
+def test_whole_decoded_portions_and_mixed_batches(folders, plain_logits, name, dtype):
+    """The same requests whole, with the last tokens decoded one by one, in portions down to two tokens, and mixed
+    (portions beside single tokens, four live at most, four state slots) in a pool that holds two of the longest: pages
+    and slots are given back and used again.  Every position against plain."""
+    reqs, prompts = make_requests(name)
+    vocab = tiny.CONFIGS[name]["vocab"]
+    block = 16 if name in ("B", "D") else 64
+    per_request = -(-max(len(t) for t in reqs.values()) // block)
+    schedules = {
+        "whole": (replay.whole(reqs), per_request),
+        "decoded": (replay.tail_decoded(reqs, tail=DECODED + 20), per_request),
+        "portions": (replay.portions(reqs), per_request),
+        "mixed": (replay.mixed(reqs, prompts, 2 * per_request * block + block, block, seed=3), 2 * per_request + 1),
+    }
+    for what, (steps, pages) in schedules.items():
+        runner = runner_for(folders[name], dtype, block, pages, max_requests=4)
+        out = replay.run_inprocess(runner, steps)
+        compare(steps, out, plain_logits[name][0], vocab, TOL[dtype], f"{name}/{dtype}/{what}", sure=plain_logits[name][1] if dtype == "bfloat16" else None)
+        assert set(runner.manager.free_pages()) == {pages} and runner.manager.live_requests() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_long_decoding_from_the_first_token(folders, name, dtype):
+    """One prompt token, then 170 tokens one by one (past page borders, past every chunk's edge and every step of the
+    query temperature), two requests side by side that started 40 steps apart; decode steps are replayed as graphs."""
+    from alofa_b200.engine.step import StepEntry
+
+    w, cfg = plain.load(folders[name])
+    a, b = tiny.tokens(name, 171, seed=50), tiny.tokens(name, 131, seed=51)
+    want_a, want_b = plain.forward(w, cfg, a), plain.forward(w, cfg, b)
+    sure_a, sure_b = (plain.sure_prefix(plain.router_margins(w, cfg, a)), plain.sure_prefix(plain.router_margins(w, cfg, b))) if dtype == "bfloat16" else (171, 131)
+    runner = runner_for(folders[name], dtype, 16, 22, max_requests=2)
+    sa, sb, errors = runner.admit(0), None, []
+    for i in range(171):
+        entries = [StepEntry(sa, [a[i]], [0])]
+        if i >= 40:
+            if sb is None:
+                sb = runner.admit(1)
+            entries.append(StepEntry(sb, [b[i - 40]], [0]))
+        rows = runner.forward(entries).float().cpu().numpy()
+        for row, want, k, sure, who in ((rows[0], want_a, i, sure_a, "first"),) + (((rows[1], want_b, i - 40, sure_b, "second"),) if i >= 40 else ()):
+            if k < sure:
+                assert_close(row, want[k], TOL[dtype], f"{who} request, token {k}")
+            errors.append(np.abs(row - want[k]).max() / max(1.0, float(np.abs(want).max())))
+    assert_most_close(errors, TOL[dtype], "long decoding")
+    runner.check_status()
+    assert runner.manager.defects() == 0
+
+
+def test_batches_and_cuts_do_not_change_a_request(folders):
+    """float32: a request's logits in portions and in a mixed batch equal, to rounding of the sums' order, those it gets alone and whole."""
+    name = "D"
+    reqs, prompts = make_requests(name)
+    vocab = tiny.CONFIGS[name]["vocab"]
+    alone = replay.collect(replay.whole(reqs), replay.run_inprocess(runner_for(folders[name], "float32", 16, 20), replay.whole(reqs)), vocab)
+    for what, steps, pages in (("portions", replay.portions(reqs), 20), ("mixed", replay.mixed(reqs, prompts, 700, 16, seed=9), 44)):
+        other = replay.collect(steps, replay.run_inprocess(runner_for(folders[name], "float32", 16, pages, max_requests=4), steps), vocab)
+        for rid in reqs:
+            assert np.abs(alone[rid] - other[rid]).max() <= 5e-6 * max(1.0, np.abs(alone[rid]).max()), f"{what} {rid}"
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_the_stream_after_every_layer(folders, name):
+    """float32: the residual stream after each layer."""
+    import alofa_b200.parts.block as block
+    from alofa_b200.engine.step import StepEntry
+
+    w, cfg = plain.load(folders[name])
+    ids = tiny.tokens(name, 30, seed=77)
+    _, want = plain.forward(w, cfg, ids, streams=True)
+    seen, original = [], block.PostnormResidual.forward
+
+    def recording(self, ctx, h, cache, writes=True):
+        original(self, ctx, h, cache, writes)
+        seen.append(h.double().cpu().numpy())
+
+    block.PostnormResidual.forward = recording
+    try:
+        runner = runner_for(folders[name], "float32", 64, 1, graphs=False)
+        runner.forward([StepEntry(runner.admit(0), ids, [0])])
+    finally:
+        block.PostnormResidual.forward = original
+    assert len(seen) == len(want) == len(cfg["layers"])
+    for k, (got, ref) in enumerate(zip(seen, want)):
+        assert_close(got, ref, TOL["float32"], f"after layer {k}")
+
+
+@pytest.mark.parametrize("name", list(tiny.CONFIGS))
+def test_greedy_generation_through_the_engine(folders, name):
+    """Engine.generate (scheduler, chunked prefill, decode graphs): float32 tokens equal plain greedy; bfloat16 tokens
+    are each within rounding of the plain maximum, up to the first close call of a router."""
+    from alofa_b200.engine.engine import Engine
+
+    w, cfg = plain.load(folders[name])
+    prompts = [tiny.tokens(name, n, seed=200 + i) for i, n in enumerate([1, 7, 40, 90, 18])]
+    want = [plain.greedy(w, cfg, p, 6) for p in prompts]
+    eng = Engine(str(folders[name]), dtype="float32", block_size=16, max_batch=3, token_budget=48, max_chunk=32, max_tokens=128)
+    assert eng.generate(prompts, max_new_tokens=6) == want
+    assert eng.stats()["defects"] == 0
+    eng16 = Engine(str(folders[name]), dtype="bfloat16", block_size=16, max_batch=3, token_budget=48, max_chunk=32, max_tokens=128)
+    for p, out in zip(prompts, eng16.generate(prompts, max_new_tokens=6)):
+        seq = list(p)
+        for tok in out:
+            if plain.sure_prefix(plain.router_margins(w, cfg, seq)) < len(seq):
+                break
+            row = plain.forward(w, cfg, seq)[-1]
+            assert row.max() - row[tok] <= 8e-2 * max(1.0, float(np.abs(row).max())), "a bfloat16 token is not near the plain maximum"
+            seq.append(tok)
+    eng16.runner.check_status()
+
+
+def test_the_programs_take_the_architecture(folders, tmp_path):
+    """bin/trace_run replays a schedule and bin/generate generates, both choosing the model by config.json."""
+    name = "C"
+    reqs, _ = make_requests(name)
+    reqs = {k: reqs[k] for k in ("r0", "r2")}
+    w, cfg = plain.load(folders[name])
+    want = {rid: plain.forward(w, cfg, t) for rid, t in reqs.items()}
+    steps = replay.portions(reqs, sizes=(40, 2, 3, 64, 1))
+    out = replay.run_trace_program(folders[name], "float32", steps, tmp_path / "out", 512)
+    compare(steps, out, want, cfg["vocab"], TOL["float32"], "trace_run")
+    prompt = tiny.tokens(name, 12, seed=5)
+    done = subprocess.run([sys.executable, str(replay.ROOT / "bin" / "generate"), "--model", str(folders[name]), "--dtype", "float32", "--prompt-ids",
+                           ",".join(map(str, prompt)), "--max-new-tokens", "5", "--max-tokens", "64", "--json"], capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert json.loads(done.stdout.strip().splitlines()[-1])["out_ids"] == [plain.greedy(w, cfg, prompt, 5)]
