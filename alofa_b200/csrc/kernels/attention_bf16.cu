@@ -54,6 +54,11 @@ __device__ __forceinline__ float sink_term(const float* sink, int head, float m_
   return sink ? exp2f(fmaf(sink[head], 1.4426950408889634f, -m_log2)) : 0.f;
 }
 
+// How far back the query at position pos sees, itself included (0: every key).  A negative `window` is a mask in chunks of
+// that many positions counted from the sequence's start: the query sees the keys of its own chunk, which is a window of
+// pos % chunk + 1 keys.  A window's start never moves back as the position grows, whichever kind it is.
+__device__ __forceinline__ int window_at(int window, int pos) { return window >= 0 ? window : pos % (-window) + 1; }
+
 #include "attention_prefill_tc.cuh"
 
 // Copy keys [j0, j0 + 64) of one KV head, keys and values, into shared tiles
@@ -143,7 +148,7 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
   const int t_first = row0 / g, t_last = last_row / g;
   int k_hi = pos0 + t_last;  // last visible key of the tile (inclusive)
   int k_lo = 0;
-  if (p.window > 0) k_lo = max(0, pos0 + t_first - p.window + 1);
+  if (p.window != 0) k_lo = max(0, pos0 + t_first - window_at(p.window, pos0 + t_first) + 1);
   if (SPLIT) {
     k_lo = max(k_lo, split * p.split_keys);
     k_hi = min(k_hi, (split + 1) * p.split_keys - 1);
@@ -231,7 +236,7 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
     // ---- visibility -------------------------------------------------------------
     const int j0 = nb * BLOCK_N;
     const bool all_visible = (j0 + BLOCK_N - 1 <= min(warp_pos_min, k_hi)) && (j0 >= k_lo) &&
-                             (p.window <= 0 || j0 > warp_pos_max - p.window);
+                             (p.window == 0 || j0 > warp_pos_max - window_at(p.window, warp_pos_max));
     if (!all_visible) {
 #pragma unroll
       for (int n = 0; n < BLOCK_N / 8; ++n) {
@@ -240,7 +245,7 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
           const int j = j0 + n * 8 + (lane & 3) * 2 + (e & 1);
           const int pos = (e < 2) ? pos_lo : pos_hi;
           bool vis = j <= pos && j >= k_lo && j <= k_hi;
-          if (p.window > 0) vis = vis && j > pos - p.window;
+          if (p.window != 0) vis = vis && j > pos - window_at(p.window, pos);
           if (!vis) s[n][e] = -INFINITY;
         }
       }
@@ -385,7 +390,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
   const int g = p.nh / p.nkv;
   const int pos = p.kv_len[seq] - 1;  // the one query position of this request
   int k_lo = 0;
-  if (p.window > 0) k_lo = max(0, pos - p.window + 1);
+  const int window = window_at(p.window, pos);  // of this one position
+  if (window > 0) k_lo = max(0, pos - window + 1);
   k_lo = max(k_lo, split * p.split_keys);
   const int k_hi = min(pos, (split + 1) * p.split_keys - 1);
   if (k_lo > k_hi) return;
@@ -496,7 +502,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
         if (LONG && lane == 0 && block + 2 * WARPS <= last) row_after = block_row(block + 2 * WARPS);
         bool values_here = true;
         attend_block<true>(
-            st, qf, kt_s, vt_s, block * BLOCK_N, lane, pos, k_lo, k_hi, p.window, p.scale_log2 CAP_ARGS(p),
+            st, qf, kt_s, vt_s, block * BLOCK_N, lane, pos, k_lo, k_hi, window, p.scale_log2 CAP_ARGS(p),
             [&] {
               if (more) {
                 __syncwarp();  // every lane has taken its scores from the key tile
@@ -513,7 +519,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
         }
         row_next = row_after;
       } else {
-        attend_block<false>(st, qf, kt_s, vt_s, block * BLOCK_N, lane, pos, k_lo, k_hi, p.window, p.scale_log2 CAP_ARGS(p));
+        attend_block<false>(st, qf, kt_s, vt_s, block * BLOCK_N, lane, pos, k_lo, k_hi, window, p.scale_log2 CAP_ARGS(p));
         if (more) {
           __syncwarp();
           fetch_padded(block + WARPS);
@@ -615,7 +621,7 @@ __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* __
   pdl_begin();
   const int P = positions[row / nh];
   int k_lo = 0;
-  if (window > 0) k_lo = max(0, P - window + 1);
+  if (window != 0) k_lo = max(0, P - window_at(window, P) + 1);
   const int s_lo = k_lo / split_keys, s_hi = P / split_keys;
   float m = -INFINITY;
   for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, partial_ml[((size_t)s * n_rows_total + row) * 2]);

@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attention_prefill_tc_kernel(con
   const int last_row = min(n_rows, row0 + TC_BM) - 1;
   const int t_first = row0 / g, t_last = last_row / g;
   const int k_hi = pos0 + t_last;  // last visible key of the tile
-  const int k_lo = p.window > 0 ? max(0, pos0 + t_first - p.window + 1) : 0;
+  const int k_lo = p.window != 0 ? max(0, pos0 + t_first - window_at(p.window, pos0 + t_first) + 1) : 0;
   const int jb0 = k_lo / TC_BN, nblk = k_hi / TC_BN - jb0 + 1;
 
   if (threadIdx.x == 0) {
@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attention_prefill_tc_kernel(con
     const int R = row0 + r;
     const bool row_ok = R < n_rows;
     const int my_pos = pos0 + (row_ok ? R / g : 0);
-    const int my_lo = p.window > 0 ? max(0, my_pos - p.window + 1) : 0;
+    const int my_lo = p.window != 0 ? max(0, my_pos - window_at(p.window, my_pos) + 1) : 0;
     uint32_t pair_phase = 0;
     auto pair_sync = [&]() -> bool {  // the two warps of a quadrant meet (bounded, like every wait here)
       mbar_arrive(&pair_bar[q4]);

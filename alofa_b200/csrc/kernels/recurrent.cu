@@ -484,7 +484,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const float* __restrict__ qkv, int ld,
                                                           const int* __restrict__ positions, const int* __restrict__ slot_map, int H, int G, int d, int dv, int maps,
                                                           int qk_norm, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps, float coef, int every,
-                                                          int n_tokens, const float* __restrict__ freq, int rot_dims, float mag, int v_from_k) {
+                                                          int n_tokens, const float* __restrict__ freq, int rot_dims, float mag, int v_from_k, int v_copies) {
   pdl_begin();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int HQ = H * maps, GK = G * maps;
@@ -536,40 +536,44 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(T* __restrict__ q_out,
     const int gi = u - HQ - GK;
     // the values: their own columns, or (v_from_k) the keys as projected, before their norm
     const float* x = v_from_k ? row + (size_t)HQ * d + (size_t)gi * d : row + (size_t)(HQ + GK) * d + (size_t)gi * dv;
-    T* to = v_cache + ((size_t)slot_map[t] * G + gi) * dv;
-    for (int c = lane; c < dv; c += 32) to[c] = from_f<T>(x[c]);
+    // v_copies > 1: the value head is written that many times side by side, one for each of the key head's keys
+    T* to = v_cache + ((size_t)slot_map[t] * G + gi) * v_copies * dv;
+    for (int c = lane; c < dv; c += 32) {
+      const T v = from_f<T>(x[c]);
+      for (int k = 0; k < v_copies; ++k) to[(size_t)k * dv + c] = v;
+    }
   }
 }
 
 ALOFA_API int alofa_qkv_prepare(void* q_out, void* k_cache, void* v_cache, const float* qkv, int ld, const int* positions, const int* slot_map, int n_tokens, int H, int G,
                                 int d, int dv, int maps, int qk_norm, const float* q_w, const float* k_w, float eps, float coef, int every, const float* freq,
-                                int rot_dims, float mag, int v_from_k, int is_bf16, cudaStream_t stream) {
+                                int rot_dims, float mag, int v_from_k, int v_copies, int is_bf16, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
   if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || maps <= 0 || (coef != 0.f && every <= 0) || rot_dims < 0 || rot_dims > d || (rot_dims & 1) || (rot_dims && !freq) ||
-      (v_from_k && (maps != 1 || dv != d)) || ld < (H + G) * maps * d + (v_from_k ? 0 : G * dv))
+      (v_from_k && (maps != 1 || dv != d)) || v_copies < 1 || ld < (H + G) * maps * d + (v_from_k ? 0 : G * dv))
     return ALOFA_ERR_ARGUMENT;
   const long long units = (long long)n_tokens * ((H + G) * maps + G);
   const unsigned blocks = (unsigned)((units + 7) / 8);
   if (is_bf16)
     launch_dep(qkv_prepare_kernel<bf16>, blocks, 256, 0, stream, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, qkv, ld, positions, slot_map, H, G, d, dv, maps, qk_norm,
-               q_w, k_w, eps, coef, every, n_tokens, freq, rot_dims, mag, v_from_k);
+               q_w, k_w, eps, coef, every, n_tokens, freq, rot_dims, mag, v_from_k, v_copies);
   else
     launch_dep(qkv_prepare_kernel<float>, blocks, 256, 0, stream, (float*)q_out, (float*)k_cache, (float*)v_cache, qkv, ld, positions, slot_map, H, G, d, dv, maps,
-               qk_norm, q_w, k_w, eps, coef, every, n_tokens, freq, rot_dims, mag, v_from_k);
+               qk_norm, q_w, k_w, eps, coef, every, n_tokens, freq, rot_dims, mag, v_from_k, v_copies);
   return launch_status();
 }
 
 // ---------------------------------------------------------------------------
 // heads_finish: what some attentions do to a head's output before the output projection, one warp per
 // (token, head), fp32.  a [T, H * maps, dv] fp32 holds the attention outputs in the order qkv_prepare
-// gave the queries ([key head][map][head of the group]).
+// gave the queries ([key head][map][head of the group]); the tensor-core attention kernels leave them in bfloat16.
 //   maps 1: o = a
 //   maps 2: o = a_1 - lambda * a_2, then o / sqrt(mean(o^2) + eps) * post   (two softmax maps over the same values)
 //   gate:   o *= sigmoid(gate[t, g_off + h])   (fp32 sums of a projection, row stride ldg)
 // out [T, H * dv] in the compute dtype, heads in their own order.
 // ---------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(256) heads_finish_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ gate, int ldg, int g_off,
+template <typename T, typename TA>
+__global__ void __launch_bounds__(256) heads_finish_kernel(T* __restrict__ out, const TA* __restrict__ a, const float* __restrict__ gate, int ldg, int g_off,
                                                            int H, int G, int dv, int maps, float lambda, float eps, float post, long long units) {
   pdl_begin();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -578,32 +582,35 @@ __global__ void __launch_bounds__(256) heads_finish_kernel(T* __restrict__ out, 
   const long long t = unit / H;
   const int h = (int)(unit - t * H), hg = H / G;
   const int g = h / hg, hh = h - g * hg;
-  const float* a1 = a + ((size_t)t * H * maps + (size_t)(g * maps) * hg + hh) * dv;
+  const TA* a1 = a + ((size_t)t * H * maps + (size_t)(g * maps) * hg + hh) * dv;
   T* o = out + ((size_t)t * H + h) * dv;
   float f = 1.f;
   if (gate) f = 1.0f / (1.0f + expf(-gate[t * ldg + g_off + h]));
   if (maps == 1) {
-    for (int c = lane; c < dv; c += 32) o[c] = from_f<T>(a1[c] * f);
+    for (int c = lane; c < dv; c += 32) o[c] = from_f<T>(to_f(a1[c]) * f);
     return;
   }
-  const float* a2 = a1 + (size_t)hg * dv;
+  const TA* a2 = a1 + (size_t)hg * dv;
   float ss = 0.f;
   for (int c = lane; c < dv; c += 32) {
-    const float v = a1[c] - lambda * a2[c];
+    const float v = to_f(a1[c]) - lambda * to_f(a2[c]);
     ss = fmaf(v, v, ss);
   }
   ss = warp_sum(ss);
   const float r = post / sqrtf(ss / (float)dv + eps);
-  for (int c = lane; c < dv; c += 32) o[c] = from_f<T>((a1[c] - lambda * a2[c]) * r * f);
+  for (int c = lane; c < dv; c += 32) o[c] = from_f<T>((to_f(a1[c]) - lambda * to_f(a2[c])) * r * f);
 }
 
-ALOFA_API int alofa_heads_finish(void* out, const float* a, const float* gate, int ldg, int g_off, int n_tokens, int H, int G, int dv, int maps, float lambda, float eps,
-                                 float post, int is_bf16, cudaStream_t stream) {
+// a_bf16: the maps' outputs are bfloat16 (out then is too), else fp32.
+ALOFA_API int alofa_heads_finish(void* out, const void* a, const float* gate, int ldg, int g_off, int n_tokens, int H, int G, int dv, int maps, float lambda, float eps,
+                                 float post, int is_bf16, int a_bf16, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
   if (H <= 0 || G <= 0 || H % G || dv <= 0 || maps < 1 || maps > 2) return ALOFA_ERR_ARGUMENT;
   const long long units = (long long)n_tokens * H;
   const unsigned blocks = (unsigned)((units + 7) / 8);
-  if (is_bf16) launch_dep(heads_finish_kernel<bf16>, blocks, 256, 0, stream, (bf16*)out, a, gate, ldg, g_off, H, G, dv, maps, lambda, eps, post, units);
-  else launch_dep(heads_finish_kernel<float>, blocks, 256, 0, stream, (float*)out, a, gate, ldg, g_off, H, G, dv, maps, lambda, eps, post, units);
+  if (a_bf16 && !is_bf16) return ALOFA_ERR_ARGUMENT;
+  if (a_bf16) launch_dep(heads_finish_kernel<bf16, bf16>, blocks, 256, 0, stream, (bf16*)out, (const bf16*)a, gate, ldg, g_off, H, G, dv, maps, lambda, eps, post, units);
+  else if (is_bf16) launch_dep(heads_finish_kernel<bf16, float>, blocks, 256, 0, stream, (bf16*)out, (const float*)a, gate, ldg, g_off, H, G, dv, maps, lambda, eps, post, units);
+  else launch_dep(heads_finish_kernel<float, float>, blocks, 256, 0, stream, (float*)out, (const float*)a, gate, ldg, g_off, H, G, dv, maps, lambda, eps, post, units);
   return launch_status();
 }

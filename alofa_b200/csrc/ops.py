@@ -917,8 +917,8 @@ def _recurrent():
             "alofa_linear_scan": [_P, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _F, _F, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
             "alofa_gated_group_norm": [_P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P],
             "alofa_branch_norm_add": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _P],
-            "alofa_qkv_prepare": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _F, _I, _P, _I, _F, _I, _I, _P],
-            "alofa_heads_finish": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _I, _P],
+            "alofa_qkv_prepare": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _F, _I, _P, _I, _F, _I, _I, _I, _P],
+            "alofa_heads_finish": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _I, _I, _P],
         }
         for name, args in sigs.items():
             fn = getattr(lib, name)
@@ -1052,7 +1052,7 @@ def branch_norm_add(h, ya, wa, yb, wb, eps: float, scale: float) -> None:
 
 
 def qkv_prepare(q_out, k_cache, v_cache, qkv, positions, slot_map, heads: int, kv_heads: int, d: int, dv: int, qk_norm: bool, eps: float, coef: float, every: int,
-                freq=None, rot_dims: int = 0, maps: int = 1, q_weight=None, k_weight=None, magnitude: float = 1.0, values_from_keys: bool = False) -> None:
+                freq=None, rot_dims: int = 0, maps: int = 1, q_weight=None, k_weight=None, magnitude: float = 1.0, values_from_keys: bool = False, v_copies: int = 1) -> None:
     """From the fp32 sums of a stacked projection whose rows start [q | k | v]
     (more columns may follow): q and k divided by their root mean square per
     head (``qk_norm``) and multiplied by ``q_weight`` / ``k_weight`` (fp32
@@ -1065,12 +1065,15 @@ def qkv_prepare(q_out, k_cache, v_cache, qkv, positions, slot_map, heads: int, k
     per head; the queries are written as ``[key head][map][head of the
     group]``, so that a kernel which gives query unit ``i`` the key unit ``i //
     (heads / kv_heads)`` pairs map with map.  ``values_from_keys``: there are
-    no v columns, the values are the keys as projected (before their norm)."""
+    no v columns, the values are the keys as projected (before their norm).
+    ``v_copies`` > 1: every value head is written that many times side by side
+    (the value cache then has ``kv_heads * v_copies`` heads), for kernels that
+    want a value head for each key head."""
     n = qkv.shape[0]
     dt = q_out.dtype
     f32 = torch.float32
     need = (heads + kv_heads) * maps * d + (0 if values_from_keys else kv_heads * dv)
-    if (qkv.shape[1] < need or tuple(q_out.shape) != (n, heads * maps * d) or tuple(k_cache.shape[1:]) != (kv_heads * maps, d) or tuple(v_cache.shape[1:]) != (kv_heads, dv)
+    if (qkv.shape[1] < need or tuple(q_out.shape) != (n, heads * maps * d) or tuple(k_cache.shape[1:]) != (kv_heads * maps, d) or tuple(v_cache.shape[1:]) != (kv_heads * v_copies, dv)
             or (q_weight is not None and q_weight.shape[0] != d) or (k_weight is not None and k_weight.shape[0] != d)):
         raise AlofaError("invalid_argument", "qkv_prepare sizes disagree", f"qkv={tuple(qkv.shape)} q={tuple(q_out.shape)} k={tuple(k_cache.shape)} v={tuple(v_cache.shape)}")
     _done(
@@ -1078,7 +1081,7 @@ def qkv_prepare(q_out, k_cache, v_cache, qkv, positions, slot_map, heads: int, k
                                        _dev(positions, "positions", torch.int32), _dev(slot_map, "slot_map", torch.int32), n, heads, kv_heads, d, dv, int(maps),
                                        1 if qk_norm else 0, _dev(q_weight, "q_weight", f32) if q_weight is not None else None,
                                        _dev(k_weight, "k_weight", f32) if k_weight is not None else None, float(eps), float(coef), int(every),
-                                       _dev(freq, "freq", f32) if rot_dims else None, int(rot_dims), float(magnitude), 1 if values_from_keys else 0,
+                                       _dev(freq, "freq", f32) if rot_dims else None, int(rot_dims), float(magnitude), 1 if values_from_keys else 0, int(v_copies),
                                        _is_bf16(q_out, "q_out"), _stream()),
         "qkv_prepare", f"heads={heads} kv_heads={kv_heads} d={d} dv={dv} maps={maps}",
     )
@@ -1086,7 +1089,7 @@ def qkv_prepare(q_out, k_cache, v_cache, qkv, positions, slot_map, heads: int, k
 
 def heads_finish(out, a, heads: int, kv_heads: int, dv: int, maps: int = 1, difference: float = 0.0, eps: float = 0.0, post: float = 1.0, gate=None, g_off: int = 0) -> None:
     """What stands between some attentions and their output projection, fp32:
-    ``a`` fp32 [T, heads * maps * dv] holds the attention outputs in the order
+    ``a`` [T, heads * maps * dv] (fp32, or bfloat16 like ``out``) holds the attention outputs in the order
     :func:`qkv_prepare` gave the queries.  ``maps`` 2: ``o = a_1 - difference *
     a_2``, then ``o / sqrt(mean(o^2) + eps) * post`` per head; ``gate`` (fp32
     [T, ld], sums of a projection): ``o *= sigmoid(gate[t, g_off + h])``.  out
@@ -1094,9 +1097,9 @@ def heads_finish(out, a, heads: int, kv_heads: int, dv: int, maps: int = 1, diff
     n = a.shape[0]
     if tuple(a.shape) != (n, heads * maps * dv) or tuple(out.shape) != (n, heads * dv) or (gate is not None and (gate.shape[0] != n or g_off + heads > gate.shape[1])):
         raise AlofaError("invalid_argument", "heads_finish sizes disagree", f"a={tuple(a.shape)} out={tuple(out.shape)}")
-    _done(_recurrent().alofa_heads_finish(_dev(out, "out"), _dev(a, "a", torch.float32), _dev(gate, "gate", torch.float32) if gate is not None else None,
+    _done(_recurrent().alofa_heads_finish(_dev(out, "out"), _dev(a, "a"), _dev(gate, "gate", torch.float32) if gate is not None else None,
                                           gate.shape[1] if gate is not None else 0, g_off, n, heads, kv_heads, dv, maps, float(difference), float(eps), float(post),
-                                          _is_bf16(out, "out"), _stream()), "heads_finish", f"heads={heads} dv={dv} maps={maps}")
+                                          _is_bf16(out, "out"), _is_bf16(a, "a"), _stream()), "heads_finish", f"heads={heads} dv={dv} maps={maps}")
 
 
 def _hyper():

@@ -28,12 +28,15 @@ class PagedAttend:
     """Attention of a step's rows over a paged key/value cache, shared by the
     mixers that keep one: which kernel runs, and how a decode step's keys are
     split over CTAs.  The mixer gives ``nh``, ``nkv``, ``hd`` (keys and values
-    alike), ``q_dim``, ``window``, ``scale``, ``softcap`` (0: none) and ``sink``
+    alike), ``q_dim``, ``window``, ``scale``, ``softcap`` (0: none), ``sink``
     (None, or a score per head that the softmax's denominator holds beside the
-    keys': the kernel that completes a row's sum adds it)."""
+    keys': the kernel that completes a row's sum adds it) and ``chunk`` (0, or
+    the size of the chunks, counted from the sequence's start, that a query
+    does not see out of; the kernels take it as a negative window)."""
 
     softcap = 0.0
     sink = None
+    chunk = 0
 
     # Keys per CTA, at least, when a decode-only step splits each request's keys: four 64-key
     # blocks, one per warp.  Splits grow in steps of this (a warp then takes several blocks in
@@ -112,10 +115,10 @@ class PagedAttend:
             if splits:
                 po = ctx.buf((splits, ctx.n_tokens * self.nh, self.hd), torch.float32)
                 pml = ctx.buf((splits, ctx.n_tokens * self.nh, 2), torch.float32)
-            unmerged = ctx.decode_only and 1 < splits <= self.MERGE_IN_PRODUCT_SPLITS and self.nh // self.nkv <= 16 and ctx.n_tokens <= 16 and self.sink is None
+            unmerged = ctx.decode_only and 1 < splits <= self.MERGE_IN_PRODUCT_SPLITS and self.nh // self.nkv <= 16 and ctx.n_tokens <= 16 and self.sink is None and not self.chunk
             ops.attention_bf16(
                 out, q, cache.k, cache.v, ctx.q_start, ctx.kv_len, ctx.positions, group.block_table, group.page_size, ctx.n_seqs, ctx.max_q_len,
-                self.nh, self.nkv, self.hd, self.window, self.scale, splits, per_split, po, pml, longest, ctx.status, combine=not unmerged, softcap=self.softcap,
+                self.nh, self.nkv, self.hd, -self.chunk if self.chunk else self.window, self.scale, splits, per_split, po, pml, longest, ctx.status, combine=not unmerged, softcap=self.softcap,
                 sink=self.sink,
             )
             if unmerged:
@@ -123,7 +126,7 @@ class PagedAttend:
             return out
         ops.paged_attention_generic(
             out, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size,
-            self.nh, self.nkv, self.hd, self.window, self.scale, self.softcap, None, self.sink,
+            self.nh, self.nkv, self.hd, self.window, self.scale, self.softcap, None, self.sink, self.chunk,
         )
         return out
 

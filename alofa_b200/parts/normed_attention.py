@@ -95,11 +95,15 @@ class NormedAttention(PagedAttend, Part):
         self.q_dim, self.k_dim = self.heads * self.maps * self.dim, self.kv_heads * self.maps * self.dim
         self.v_dim = 0 if self.values_from_keys else self.kv_heads * self.vdim  # columns of the stacked projection
         self.rows = self.q_dim + self.k_dim + self.v_dim + (self.heads if self.gate else 0)  # [q | k | v | gate]
-        self.nh, self.nkv, self.hd = self.heads, self.kv_heads, self.dim  # what the shared choice of kernels goes by (keys and values alike only)
+        # the bfloat16 tensor-core kernels take keys and values of one size and as many value heads as key heads: with several maps a
+        # head the values are then kept once per map (the every-size kernel reads one value head for all of a key head's maps)
+        self.tensor_cores = rt.dtype == torch.bfloat16 and self.dim == self.vdim and ops.attention_bf16_supported(self.dim)
+        self.v_copies = self.maps if self.tensor_cores else 1
+        self.nh, self.nkv, self.hd = self.heads * self.maps, self.kv_heads * self.maps, self.dim  # what the shared choice of kernels goes by (keys and values alike only)
 
     def cache_spec(self):
         # a chunk never reaches further back than its own size: the pages behind it are given back like a window's
-        return PagedKV(self.kv_heads * self.maps, self.dim, self.chunk or self.window, self.vdim, self.kv_heads)
+        return PagedKV(self.kv_heads * self.maps, self.dim, self.chunk or self.window, self.vdim, self.kv_heads * self.v_copies)
 
     def scratch_row_bytes(self) -> int:
         return 4 * self.rows + 4 * self.q_dim + 4 * (self.maps + 1) * self.heads * self.vdim + 8 * self.hidden
@@ -157,13 +161,16 @@ class NormedAttention(PagedAttend, Part):
         rotated = self.rot_dims > 0
         ops.qkv_prepare(q, cache.k, cache.v, sums, ctx.positions, group.slot_map, self.heads, self.kv_heads, self.dim, self.vdim, self.qk_norm, self.eps, self.coef, self.every,
                         self.position.frequencies() if rotated else None, self.rot_dims, self.maps, self.q_weight, self.k_weight,
-                        float(getattr(self.position, "magnitude", 1.0)) if rotated else 1.0, self.values_from_keys)
+                        float(getattr(self.position, "magnitude", 1.0)) if rotated else 1.0, self.values_from_keys, self.v_copies)
         g_off = self.q_dim + self.k_dim + self.v_dim  # the gates' column in the stacked projection's sums
-        if self.dim == self.vdim and self.maps == 1 and not self.chunk:
+        if self.tensor_cores or (self.dim == self.vdim and self.maps == 1 and not self.chunk):
             out = self.attend(ctx, q, cache, group)  # the tensor-core kernels in bfloat16 for the head sizes they are built for, else the every-size kernel
-            if self.gate:
-                if not isinstance(out, torch.Tensor):
-                    out = out.rows()
+            if (self.gate or self.maps > 1) and not isinstance(out, torch.Tensor):
+                out = out.rows()
+            if self.maps > 1:
+                a, out = out, ctx.buf((n, self.heads * self.vdim), dt)
+                ops.heads_finish(out, a, self.heads, self.kv_heads, self.vdim, self.maps, self.difference, self.eps, 1.0 - self.diff, sums if self.gate else None, g_off)
+            elif self.gate:
                 ops.head_gate(out, sums, g_off, self.heads, self.vdim)
         else:
             # the every-size kernel; what is still to be combined or gated stays fp32 until it has been

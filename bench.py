@@ -5,6 +5,7 @@
     python bench.py --design kotutar [--size 1k|2k]     (another line: that design beside Qwen2 at equal layer sizes)
     python bench.py --design darolix [--size 1k|2k]     (another line: that design beside Kotutar at equal layer sizes)
     python bench.py --design dibulix [--size 1k|2k]     (another line: that design beside Darolix at equal layer sizes)
+    python bench.py --design kikerax [--size 1k|2k]     (another line: that design beside Darolix at equal layer sizes)
 
 The default run has the layer sizes of the Qwen2.5-0.5B shape with random
 weights, a batch of 8 requests with 2,048-token prompts inside a 4,096-token
@@ -558,6 +559,52 @@ def dibulix_numbers(z: dict, b: dict) -> dict:
             "state_bytes_per_request": 2 * state_bytes + window_bytes}
 
 
+# --design kikerax: differential attention in chunks and attention + gated linear recurrent unit layers in turn, dense and
+# routed feed-forwards in turn, beside the Darolix design at the same width, layers, heads, experts and vocabulary.  Inner
+# sizes after published models of the kind: two maps a head with keys and values of 128 over chunks of 1,024 tokens, a quarter
+# of each map turned; attention heads of 128 beside a recurrent unit 4/3 as wide as the model in blocks of 256 channels with
+# four taps; four groups of experts of which two are kept.
+KIKERAX_SIZES = {
+    "1k": dict(kv_heads=2, att_dim=128, att_rot=32, chunk=1024, lru_width=1280, lru_block=256, conv=4, groups=4, keep=2),
+    "2k": dict(kv_heads=4, att_dim=128, att_rot=32, chunk=1024, lru_width=2560, lru_block=256, conv=4, groups=8, keep=4),
+}
+
+
+def kikerax_config(z: dict, b: dict):
+    """Differential attention with a dense feed-forward and attention beside the recurrent unit with routed experts, in turn."""
+    from alofa_b200.models.kikerax import DifferentialConfig, FeedForwardConfig, KeyedAttentionConfig, KikeraxConfig, KikeraxLayer, ParallelConfig, RecurrentConfig
+
+    d = b["att_dim"]
+    attention = DifferentialConfig(z["heads"], b["kv_heads"], d, d, d ** -0.5, 0.6, {"base": 1e4, "dims": b["att_rot"], "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}},
+                                   b["chunk"])
+    pair = ParallelConfig(KeyedAttentionConfig(z["heads"], b["kv_heads"], d, d, d ** -0.5, 50.0, {"coef": 0.3, "every": 128}),
+                          RecurrentConfig(b["lru_width"], b["lru_width"] // b["lru_block"], b["conv"]), 0.6, 0.9)
+    dense = FeedForwardConfig("dense", z["ff"])
+    routed = FeedForwardConfig("moe", z["expert_ff"], z["experts"], z["top"], 2.0, {"count": b["groups"], "keep": b["keep"]}, z["shared_ff"])
+    layers = [KikeraxLayer("attention", attention, dense) if i % 2 == 0 else KikeraxLayer("parallel", pair, routed) for i in range(z["layers"])]
+    return KikeraxConfig(z["vocab"], z["width"], 1e-6, 30.0, layers)
+
+
+def kikerax_numbers(z: dict, b: dict) -> dict:
+    """Bytes a decode step reads and flops a token costs for the Kikerax sizes (bf16 weights and caches, fp32 states and gates).
+    The chunked layers' keys never reach further back than a chunk, so their share of a decode step is counted as state."""
+    w, h, d, g = z["width"], z["heads"], b["att_dim"], b["kv_heads"]
+    diff = w * (2 * h * d + 2 * g * d + g * d + h) + h * d * w
+    keyed = w * (h * d + g * d + h) + h * d * w
+    W, bs = b["lru_width"], b["lru_block"]
+    lru = 3 * w * W + W * b["conv"]
+    gates = 2 * W * bs  # fp32
+    n_att, n_pair = (z["layers"] + 1) // 2, z["layers"] // 2
+    expert = 3 * w * z["expert_ff"]
+    routed_all, routed_tok = z["experts"] * expert + 3 * w * z["shared_ff"] + z["experts"] * w, z["top"] * expert + 3 * w * z["shared_ff"] + z["experts"] * w
+    params_all = n_att * (diff + 2 * w * z["ff"]) + n_pair * (keyed + lru + routed_all)
+    per_token = n_att * (diff + 2 * w * z["ff"]) + n_pair * (keyed + lru + gates + routed_tok)
+    state_bytes = 4 * n_pair * W * b["conv"]
+    chunk_bytes = 2 * n_att * (b["chunk"] // 2) * (2 * g * d + g * d)  # half a chunk on average
+    return {"weight_bytes": 2 * (params_all + z["vocab"] * w) + 4 * n_pair * gates, "kv_bytes_per_token": n_pair * 2 * g * d * 2, "flops_per_token": 2.0 * per_token,
+            "attn_flops_per_pair": n_pair * 4.0 * h * d, "head_flops": 2.0 * w * z["vocab"], "state_bytes_per_request": 2 * state_bytes + chunk_bytes}
+
+
 class KernelClock:
     """Times every kernel call of the package's ops module with its own pair of CUDA events during one
     step (run outright, no graph), and sets each beside the time its own operands allow: the larger of
@@ -565,7 +612,7 @@ class KernelClock:
 
     PRODUCTS = ("gemm_tc", "gemm_generic", "gemm_batched", "gemm_tc_rope")
     ATTENTION = ("attention_bf16", "latent_attention_bf16", "latent_attention", "paged_attention_generic")
-    STATE = ("linear_scan", "causal_conv", "delta_scan", "min_gru")  # read and leave a state per request
+    STATE = ("linear_scan", "causal_conv", "delta_scan", "min_gru", "lru_scan")  # read and leave a state per request
 
     def __init__(self, peaks: dict):
         self.peaks = peaks
@@ -616,6 +663,19 @@ class KernelClock:
         elif name == "min_gru":
             out, n_seqs = args[0], args[8]
             byts = out.numel() * (12 + out.element_size()) + 8 * n_seqs * out.shape[1]
+        elif name == "lru_scan":
+            # out, a, b, y, ., ., state, q_start, slots, n_seqs: decays, driven inputs and the other branch once, the outputs once, the live requests' states read and written
+            out, n_seqs = args[0], args[9]
+            byts = out.numel() * (12 + out.element_size()) + 8 * n_seqs * out.shape[1]
+        elif name == "lru_gates":
+            # a, b, u, wa, wi, ...: 32-bit by the design: two block-diagonal products on the fp32 pipe, against the nominal fp32 rate
+            a, wa = args[0], args[3]
+            import torch as _t
+
+            fp32_rate = _t.cuda.get_device_properties(0).multi_processor_count * 128 * 2 * 1.965e9
+            flops = 4.0 * a.shape[0] * a.shape[1] * wa.shape[1]
+            byts = 12 * a.numel() + 8 * wa.numel()
+            return max(flops / fp32_rate, byts / (self.peaks["hbm_gbs"] * 1e9)) * 1e6, flops, byts
         elif name == "hyper_connect":
             # the streams read once, and written once when a sublayer's output is owed; that output, the next input and the sum once each
             streams = args[0]
@@ -799,15 +859,18 @@ def run_designs(args) -> dict:
     """Prefill and decode of a design beside its closest existing design at equal layer sizes (Kotutar
     beside Qwen2, Darolix beside Kotutar, Dibulix beside Darolix), and the kernels of one step of each
     against their own rooflines."""
-    from alofa_b200.models import darolix, dibulix, kotutar, qwen2
+    from alofa_b200.models import darolix, dibulix, kikerax, kotutar, qwen2
 
-    pair = {"dibulix": "Dibulix design beside Darolix", "darolix": "Darolix design beside Kotutar", "kotutar": "Kotutar design beside Qwen2"}[args.design]
+    pair = {"kikerax": "Kikerax design beside Darolix", "dibulix": "Dibulix design beside Darolix", "darolix": "Darolix design beside Kotutar", "kotutar": "Kotutar design beside Qwen2"}[args.design]
     out = {"metric": f"prefill and decode of the {pair} at equal layer sizes", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
            "prompt_tokens": PROMPT_LEN, "context": CONTEXT, "steps": args.steps, "warmup": args.warmup, "sizes": {}}
     for size in ([args.size] if args.size else sorted(DESIGN_SIZES)):
         z = DESIGN_SIZES[size]
         row = {"sizes": z}
-        if args.design == "dibulix":
+        if args.design == "kikerax":
+            row["kikerax_sizes"], row["darolix_sizes"] = KIKERAX_SIZES[size], DAROLIX_SIZES[size]
+            arms = (("kikerax", kikerax.NAME, kikerax_config(z, KIKERAX_SIZES[size])), ("darolix", darolix.NAME, darolix_config(z, DAROLIX_SIZES[size])))
+        elif args.design == "dibulix":
             row["dibulix_sizes"], row["darolix_sizes"] = DIBULIX_SIZES[size], DAROLIX_SIZES[size]
             arms = (("dibulix", dibulix.NAME, dibulix_config(z, DIBULIX_SIZES[size])), ("darolix", darolix.NAME, darolix_config(z, DAROLIX_SIZES[size])))
         elif args.design == "darolix":
@@ -816,7 +879,9 @@ def run_designs(args) -> dict:
         else:
             arms = (("kotutar", kotutar.NAME, kotutar_config(z)), ("qwen2", qwen2.NAME, qwen2_config_like(z)))
         for design, name, cfg in arms:
-            if design == "dibulix":
+            if design == "kikerax":
+                n = kikerax_numbers(z, KIKERAX_SIZES[size])
+            elif design == "dibulix":
                 n = dibulix_numbers(z, DIBULIX_SIZES[size])
             elif design == "darolix":
                 n = darolix_numbers(z, DAROLIX_SIZES[size])
@@ -854,7 +919,7 @@ def main() -> int:
     ap.add_argument("--phase", choices=["all", "decode", "prefill"], default="all", help="profiling aid: run only one part; the JSON line then lacks the others")
     ap.add_argument("--shape", choices=sorted(SHAPES), default="0.5b", help="whose layer sizes the headline run has")
     ap.add_argument("--no-extra", dest="extra", action="store_false", help="leave out the measurements beside the headline (long contexts, the 1.5B and 7B shapes)")
-    ap.add_argument("--design", choices=["kotutar", "darolix", "dibulix"], help="instead of the headline run: this design beside its closest existing one (Qwen2 for kotutar, Kotutar for darolix, Darolix for dibulix) at equal layer sizes (prefill, decode, kernels against their rooflines)")
+    ap.add_argument("--design", choices=["kotutar", "darolix", "dibulix", "kikerax"], help="instead of the headline run: this design beside its closest existing one (Qwen2 for kotutar, Kotutar for darolix, Darolix for dibulix and kikerax) at equal layer sizes (prefill, decode, kernels against their rooflines)")
     ap.add_argument("--size", choices=sorted(DESIGN_SIZES), help="with --design: one of the sizes only")
     args = ap.parse_args()
     if args.impl == "reference":

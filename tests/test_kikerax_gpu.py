@@ -81,8 +81,9 @@ class PagedCase:
         return np.array([self.table[r, j // self.page] * self.page + j % self.page for j in range(lo, hi)], dtype=np.int32)
 
 
-def attend(case, m, maps, w, rows, spans, dtype, eps, prefix="a."):
-    """The kernels' pipeline over the rows ``spans`` = [(request, lo, hi)] of ``rows[request]`` in one step."""
+def attend(case, m, maps, w, rows, spans, dtype, eps, prefix="a.", tensor_cores=False):
+    """The kernels' pipeline over the rows ``spans`` = [(request, lo, hi)] of ``rows[request]`` in one step;
+    ``tensor_cores``: the bfloat16 tensor-core attention kernels (a value head per key, the chunk as a negative window)."""
     from alofa_b200.csrc import ops
 
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
@@ -96,19 +97,37 @@ def attend(case, m, maps, w, rows, spans, dtype, eps, prefix="a."):
     freq, mag = plain.rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling")) if rot else (None, 1.0)
     temp = m.get("q_temp") or {"coef": 0.0, "every": 1}
     ops.qkv_prepare(q, case.k, case.v, dev(sums, F32), positions, slot_map, H, G, d, dv, True, eps, temp["coef"], temp["every"],
-                    dev(freq.astype(np.float32)) if rot else None, rot["dims"] if rot else 0, maps, dev(w[prefix + "q.norm"], F32), dev(w[prefix + "k.norm"], F32), mag, maps == 1)
-    a = torch.empty((n, H * maps * dv), dtype=F32, device="cuda")
-    ops.paged_attention_generic(a, q, case.k, case.v, positions, seq, case.table_dev, case.page, H * maps, G * maps, d, None, m["scale"], m.get("softcap") or 0.0, dv, None,
-                                (m.get("mask") or {}).get("size", 0), maps)
+                    dev(freq.astype(np.float32)) if rot else None, rot["dims"] if rot else 0, maps, dev(w[prefix + "q.norm"], F32), dev(w[prefix + "k.norm"], F32), mag, maps == 1, maps if tensor_cores else 1)
+    chunk = (m.get("mask") or {}).get("size", 0)
+    if tensor_cores:
+        a = torch.empty((n, H * maps * dv), dtype=BF16, device="cuda")
+        counts = [hi - lo for _, lo, hi in spans]
+        q_start = dev(np.concatenate([[0], np.cumsum(counts)]).astype(np.int32))
+        kv_len = dev(np.array([hi for _, _, hi in spans], dtype=np.int32))
+        table = dev(case.table[[r for r, _, _ in spans]])
+        longest = max(hi for _, _, hi in spans)
+        splits, po, pml = 0, None, None
+        if max(counts) == 1:  # a decode step: every request's keys in splits of 256
+            splits = -(-longest // 256)
+            po = torch.empty((splits, n * H * maps, dv), dtype=F32, device="cuda")
+            pml = torch.empty((splits, n * H * maps, 2), dtype=F32, device="cuda")
+        status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        ops.attention_bf16(a, q, case.k, case.v, q_start, kv_len, positions, table, case.page, len(spans), max(counts), H * maps, G * maps, d, -chunk if chunk else None,
+                           m["scale"], splits, 256, po, pml, longest, status, softcap=m.get("softcap") or 0.0)
+        assert int(status.sum()) == 0
+    else:
+        a = torch.empty((n, H * maps * dv), dtype=F32, device="cuda")
+        ops.paged_attention_generic(a, q, case.k, case.v, positions, seq, case.table_dev, case.page, H * maps, G * maps, d, None, m["scale"], m.get("softcap") or 0.0, dv, None,
+                                    chunk, maps)
     out = torch.empty((n, H * dv), dtype=dtype, device="cuda")
     lam = plain.difference_weight(w, prefix, m["diff"]) if maps == 2 else 0.0
     ops.heads_finish(out, a, H, G, dv, maps, lam, eps, 1.0 - m["diff"] if maps == 2 else 1.0, dev(sums, F32), sums.shape[1] - H)
     return out.float().cpu().numpy()
 
 
-def in_steps(case, m, maps, w, rows, dtype, eps, cuts):
+def in_steps(case, m, maps, w, rows, dtype, eps, cuts, tensor_cores=False):
     """Every request whole in one step; then again from an empty cache in portions of ``cuts`` (1: decoding) with all requests in every step."""
-    whole = attend(case, m, maps, w, rows, [(r, 0, n) for r, n in enumerate(case.lengths)], dtype, eps)
+    whole = attend(case, m, maps, w, rows, [(r, 0, n) for r, n in enumerate(case.lengths)], dtype, eps, tensor_cores=tensor_cores)
     split = np.cumsum([0] + list(case.lengths))
     out = [[whole[split[r] : split[r + 1]] for r in range(len(rows))]]
     case.k.fill_(7.0)
@@ -121,7 +140,7 @@ def in_steps(case, m, maps, w, rows, dtype, eps, cuts):
                 c = min(cuts[(step + r) % len(cuts)], n - at[r])
                 spans.append((r, at[r], at[r] + c))
         step += 1
-        res, k = attend(case, m, maps, w, rows, spans, dtype, eps), 0
+        res, k = attend(case, m, maps, w, rows, spans, dtype, eps, tensor_cores=tensor_cores), 0
         for r, lo, hi in spans:
             got[r].append(res[k : k + hi - lo])
             k += hi - lo
@@ -154,6 +173,29 @@ def test_differential_attention_in_chunks_over_paged_keys(dtype, H, G, d, dv, ch
         for what, got in zip(("whole", f"portions of {cuts}"), in_steps(case, m, 2, w, rows, dtype, eps, cuts)):
             for r, n in enumerate(lengths):
                 assert_close(got[r], want[r], KERNEL_TOL[dtype], f"{what}: request of {n} tokens")
+
+
+@pytest.mark.parametrize("H,G,d,chunk,page", [(2, 1, 64, 64, 64), (4, 2, 64, 100, 64), (2, 2, 128, 48, 64), (3, 1, 48, 21, 16), (2, 1, 96, 130, 64), (2, 1, 64, None, 64)])
+def test_chunks_and_two_maps_on_the_tensor_core_kernels(H, G, d, chunk, page):
+    """bfloat16, keys and values of one size: the tcgen05 / mma.sync prompt kernels and the decode kernels with the chunk
+    as their window and a value head for each of a key head's maps; whole prompts, portions and decoding in key splits."""
+    rng = np.random.default_rng(13)
+    m = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": 2.0 / np.sqrt(d), "diff": 0.4, "rot": {"base": 1000.0, "dims": d // 2, "scaling": None}}
+    if chunk:
+        m["mask"] = {"size": chunk}
+    w, width = picking_weights(rng, m, 2)
+    for n in ("lq1", "lk1", "lq2", "lk2"):  # lambda near diff, as models of the kind start: these kernels hand the two maps' outputs on in bfloat16,
+        w["a." + n] = 0.3 * w["a." + n]  # and where lambda a_2 all but cancels a_1 the norm after the difference magnifies that rounding
+    c = chunk or 50
+    lengths = sorted({1, 2, 63, 64, 65, c - 1, c, c + 1, 2 * c + 1, 257, 300})
+    rows = [rounded(rng.standard_normal((n, width)), F32) for n in lengths]
+    eps = 1e-5
+    want = [plain.differential_attention(w, "a.", m, x, eps) for x in rows]
+    for cuts in ((1,), (5, 2, 64, 3, 2, 130)):
+        case = PagedCase(rng, lengths, page, 2 * G, d, 2 * G, d, BF16)
+        for what, got in zip(("whole", f"portions of {cuts}"), in_steps(case, m, 2, w, rows, BF16, eps, cuts, tensor_cores=True)):
+            for r, n in enumerate(lengths):
+                assert_close(got[r], want[r], KERNEL_TOL[BF16], f"{what}: request of {n} tokens")
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
