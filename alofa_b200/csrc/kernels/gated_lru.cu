@@ -12,49 +12,69 @@
 #include "common.cuh"
 
 __device__ __forceinline__ float lru_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float lru_softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
 // ---------------------------------------------------------------------------
 // lru_gates: u [T, W] fp32; wa, wi [B][bs][bs] fp32 stored [block][in][out] (the transposes of the
 // checkpoint's [out, in], so that the threads of a warp read neighbouring numbers); ba, bi [W];
-// rate [W] = -c * softplus(lam), made once at load.  Writes a [T, W] and the driven input
-// b = sqrt(1 - a^2) * i * u [T, W].  A block takes LRU_TT tokens, one block of the channels and
+// lam [W] and c: log a = -c * r * softplus(lam).  Writes a [T, W] and the driven input
+// b = sqrt(1 - a^2) * i * u [T, W].  A block takes TT tokens, one block of the channels and
 // LRU_OT of its outputs, a thread per output; the tokens' inputs lie in shared memory.
 // ---------------------------------------------------------------------------
-constexpr int LRU_TT = 8;
+constexpr int LRU_TT = 8;       // tokens a block of the kernel for a handful of tokens takes
+constexpr int LRU_TT_LONG = 32; // and of this kernel over prompt portions: every weight is read once for so many tokens
 constexpr int LRU_OT = 128;
 
+template <int TT>
 __global__ void __launch_bounds__(LRU_OT) lru_gates_kernel(float* __restrict__ a_out, float* __restrict__ b_out, const float* __restrict__ u, const float* __restrict__ wa,
                                                            const float* __restrict__ wi, const float* __restrict__ ba, const float* __restrict__ bi,
-                                                           const float* __restrict__ rate, int n_tokens, int W, int bs) {
-  extern __shared__ float lru_us[];  // [LRU_TT][bs]
+                                                           const float* __restrict__ lam, float decay_scale, int n_tokens, int W, int bs) {
+  extern __shared__ __align__(16) float lru_us[];  // [TT][bs]
   pdl_begin();
-  const int t0 = blockIdx.x * LRU_TT, blk = blockIdx.y, o = blockIdx.z * LRU_OT + threadIdx.x;
-  const int live = min(LRU_TT, n_tokens - t0);
-  for (int e = threadIdx.x; e < LRU_TT * bs; e += LRU_OT) {
+  const int t0 = blockIdx.x * TT, blk = blockIdx.y, o = blockIdx.z * LRU_OT + threadIdx.x;
+  const int live = min(TT, n_tokens - t0);
+  for (int e = threadIdx.x; e < TT * bs; e += LRU_OT) {
     const int r = e / bs, c = e - r * bs;
     lru_us[e] = r < live ? u[(size_t)(t0 + r) * W + blk * bs + c] : 0.f;
   }
   __syncthreads();
   if (o >= bs) return;
-  float sa[LRU_TT], si[LRU_TT];
+  float sa[TT], si[TT];
 #pragma unroll
-  for (int r = 0; r < LRU_TT; ++r) sa[r] = si[r] = 0.f;
+  for (int r = 0; r < TT; ++r) sa[r] = si[r] = 0.f;
   const float* pa = wa + (size_t)blk * bs * bs + o;
   const float* pi = wi + (size_t)blk * bs * bs + o;
-#pragma unroll 4
-  for (int k = 0; k < bs; ++k) {
-    const float va = pa[(size_t)k * bs], vi = pi[(size_t)k * bs];
+  if ((bs & 3) == 0) {
+    // four inputs at a time: a token's four come in one 16-byte load from shared memory (one a thread per input made the
+    // load/store unit, not the multiply-adds, the limit); every sum still takes its inputs in ascending order
+#pragma unroll 2
+    for (int k = 0; k < bs; k += 4) {
+      float va[4], vi[4];
 #pragma unroll
-    for (int r = 0; r < LRU_TT; ++r) {
-      const float x = lru_us[r * bs + k];
-      sa[r] = fmaf(va, x, sa[r]);
-      si[r] = fmaf(vi, x, si[r]);
+      for (int j = 0; j < 4; ++j) va[j] = pa[(size_t)(k + j) * bs], vi[j] = pi[(size_t)(k + j) * bs];
+#pragma unroll
+      for (int r = 0; r < TT; ++r) {
+        const float4 x = *reinterpret_cast<const float4*>(lru_us + r * bs + k);
+        sa[r] = fmaf(va[3], x.w, fmaf(va[2], x.z, fmaf(va[1], x.y, fmaf(va[0], x.x, sa[r]))));
+        si[r] = fmaf(vi[3], x.w, fmaf(vi[2], x.z, fmaf(vi[1], x.y, fmaf(vi[0], x.x, si[r]))));
+      }
+    }
+  } else {
+#pragma unroll 4
+    for (int k = 0; k < bs; ++k) {
+      const float va = pa[(size_t)k * bs], vi = pi[(size_t)k * bs];
+#pragma unroll
+      for (int r = 0; r < TT; ++r) {
+        const float x = lru_us[r * bs + k];
+        sa[r] = fmaf(va, x, sa[r]);
+        si[r] = fmaf(vi, x, si[r]);
+      }
     }
   }
   const int ch = blk * bs + o;
-  const float bias_a = ba[ch], bias_i = bi[ch], rt = rate[ch];
+  const float bias_a = ba[ch], bias_i = bi[ch], rt = -decay_scale * lru_softplus(lam[ch]);
 #pragma unroll
-  for (int r = 0; r < LRU_TT; ++r) {
+  for (int r = 0; r < TT; ++r) {
     if (r >= live) break;
     const float gate_r = lru_sigmoid(sa[r] + bias_a), gate_i = lru_sigmoid(si[r] + bias_i);
     const float log_a = rt * gate_r;  // never positive
@@ -66,20 +86,94 @@ __global__ void __launch_bounds__(LRU_OT) lru_gates_kernel(float* __restrict__ a
   }
 }
 
-ALOFA_API int alofa_lru_gates(float* a_out, float* b_out, const float* u, const float* wa, const float* wi, const float* ba, const float* bi, const float* rate,
-                              int n_tokens, int W, int blocks, cudaStream_t stream) {
+// The same for a handful of tokens (decode steps), where the kernel above would leave most of the device idle and every
+// thread waiting for its own weights: wa_rows, wi_rows [B][out][in] as the checkpoint has them; a warp takes an output
+// channel at a time, its lanes share the block's inputs four neighbours each (16-byte loads of the weights' rows), and
+// the lanes' shares are added in butterfly order.  The order of a sum's additions depends on the block's size alone.
+constexpr int LRU_ROWS_OUT = 32;  // outputs a CTA of eight warps takes
+
+__global__ void __launch_bounds__(256) lru_gates_rows_kernel(float* __restrict__ a_out, float* __restrict__ b_out, const float* __restrict__ u,
+                                                             const float* __restrict__ wa, const float* __restrict__ wi, const float* __restrict__ ba,
+                                                             const float* __restrict__ bi, const float* __restrict__ lam, float decay_scale, int n_tokens, int W, int bs) {
+  extern __shared__ __align__(16) float lru_rows_us[];  // [LRU_TT][bs]
+  pdl_begin();
+  const int t0 = blockIdx.x * LRU_TT, blk = blockIdx.y, o0 = blockIdx.z * LRU_ROWS_OUT;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int live = min(LRU_TT, n_tokens - t0);
+  for (int e = threadIdx.x; e < LRU_TT * bs; e += 256) {
+    const int r = e / bs, c = e - r * bs;
+    lru_rows_us[e] = r < live ? u[(size_t)(t0 + r) * W + blk * bs + c] : 0.f;
+  }
+  __syncthreads();
+  for (int o = o0 + warp; o < min(o0 + LRU_ROWS_OUT, bs); o += 8) {
+    const float4* pa = reinterpret_cast<const float4*>(wa + ((size_t)blk * bs + o) * bs);
+    const float4* pi = reinterpret_cast<const float4*>(wi + ((size_t)blk * bs + o) * bs);
+    float sa[LRU_TT], si[LRU_TT];
+#pragma unroll
+    for (int r = 0; r < LRU_TT; ++r) sa[r] = si[r] = 0.f;
+    for (int c = lane; c < bs / 4; c += 32) {
+      const float4 va = pa[c], vi = pi[c];
+#pragma unroll
+      for (int r = 0; r < LRU_TT; ++r) {
+        const float4 x = reinterpret_cast<const float4*>(lru_rows_us + r * bs)[c];
+        sa[r] = fmaf(va.w, x.w, fmaf(va.z, x.z, fmaf(va.y, x.y, fmaf(va.x, x.x, sa[r]))));
+        si[r] = fmaf(vi.w, x.w, fmaf(vi.z, x.z, fmaf(vi.y, x.y, fmaf(vi.x, x.x, si[r]))));
+      }
+    }
+    const int ch = blk * bs + o;
+    const float bias_a = ba[ch], bias_i = bi[ch], rt = -decay_scale * lru_softplus(lam[ch]);
+#pragma unroll
+    for (int r = 0; r < LRU_TT; ++r) {
+      const float za = warp_sum(sa[r]), zi = warp_sum(si[r]);
+      if (lane == 0 && r < live) {
+        const float gate_r = lru_sigmoid(za + bias_a), gate_i = lru_sigmoid(zi + bias_i);
+        const float log_a = rt * gate_r;
+        const size_t at = (size_t)(t0 + r) * W + ch;
+        a_out[at] = expf(log_a);
+        b_out[at] = sqrtf(-expm1f(2.0f * log_a)) * gate_i * lru_rows_us[r * bs + o];
+      }
+    }
+  }
+}
+
+// wa, wi: [B][in][out]; wa_rows, wi_rows: the same matrices as [B][out][in] (may be null: then every step takes the first kernel).
+ALOFA_API int alofa_lru_gates(float* a_out, float* b_out, const float* u, const float* wa, const float* wi, const float* wa_rows, const float* wi_rows, const float* ba,
+                              const float* bi, const float* lam, float decay_scale, int n_tokens, int W, int blocks, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
   if (W <= 0 || blocks <= 0 || W % blocks) return ALOFA_ERR_ARGUMENT;
   const int bs = W / blocks;
   const size_t smem = (size_t)LRU_TT * bs * sizeof(float);
   if (smem > 200 * 1024) return ALOFA_ERR_ARGUMENT;
+  if (wa_rows && wi_rows && n_tokens <= 128 && bs % 4 == 0 && W % 4 == 0) {
+    static size_t set_rows = 48 * 1024;
+    if (smem > set_rows) {
+      if (cudaFuncSetAttribute(lru_gates_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
+      set_rows = smem;
+    }
+    launch_dep(lru_gates_rows_kernel, dim3((n_tokens + LRU_TT - 1) / LRU_TT, blocks, (bs + LRU_ROWS_OUT - 1) / LRU_ROWS_OUT), 256, smem, stream, a_out, b_out, u, wa_rows,
+               wi_rows, ba, bi, lam, decay_scale, n_tokens, W, bs);
+    return launch_status();
+  }
+  // prompt portions: 32 tokens a block where their inputs fit in shared memory (with 8 every block pulled its 2 x bs x 128 weights
+  // from L2 for 8 tokens' worth of arithmetic, and L2 set the pace: 460 us for 4,096 tokens of 2,560 channels in blocks of 256)
+  const size_t smem_long = (size_t)LRU_TT_LONG * bs * sizeof(float);
+  if (n_tokens >= 8 * LRU_TT_LONG && smem_long <= 200 * 1024) {
+    static size_t set_long = 48 * 1024;
+    if (smem_long > set_long) {
+      if (cudaFuncSetAttribute(lru_gates_kernel<LRU_TT_LONG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_long) != cudaSuccess) return ALOFA_ERR_LAUNCH;
+      set_long = smem_long;
+    }
+    launch_dep(lru_gates_kernel<LRU_TT_LONG>, dim3((n_tokens + LRU_TT_LONG - 1) / LRU_TT_LONG, blocks, (bs + LRU_OT - 1) / LRU_OT), LRU_OT, smem_long, stream, a_out, b_out,
+               u, wa, wi, ba, bi, lam, decay_scale, n_tokens, W, bs);
+    return launch_status();
+  }
   static size_t set = 48 * 1024;
   if (smem > set) {
-    if (cudaFuncSetAttribute(lru_gates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
+    if (cudaFuncSetAttribute(lru_gates_kernel<LRU_TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
     set = smem;
   }
-  launch_dep(lru_gates_kernel, dim3((n_tokens + LRU_TT - 1) / LRU_TT, blocks, (bs + LRU_OT - 1) / LRU_OT), LRU_OT, smem, stream, a_out, b_out, u, wa, wi, ba, bi, rate,
-             n_tokens, W, bs);
+  launch_dep(lru_gates_kernel<LRU_TT>, dim3((n_tokens + LRU_TT - 1) / LRU_TT, blocks, (bs + LRU_OT - 1) / LRU_OT), LRU_OT, smem, stream, a_out, b_out, u, wa, wi, ba, bi, lam,
+             decay_scale, n_tokens, W, bs);
   return launch_status();
 }
 
@@ -96,7 +190,7 @@ ALOFA_API int alofa_lru_gates(float* a_out, float* b_out, const float* u, const 
 // block, which walks its (one) token from the stored state.
 // ---------------------------------------------------------------------------
 constexpr int LRU_AHEAD = 8;
-constexpr int LRU_MAX_WARPS = 16;
+constexpr int LRU_MAX_WARPS = 32;
 
 template <typename TO>
 __global__ void __launch_bounds__(LRU_MAX_WARPS * 32) lru_scan_kernel(TO* __restrict__ out, const float* __restrict__ a_in, const float* __restrict__ b_in,

@@ -1265,7 +1265,7 @@ def _gated_lru():
     if lib is None:
         lib = load_library("alofa_gated_lru", ["kernels/gated_lru.cu"])
         sigs = {
-            "alofa_lru_gates": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+            "alofa_lru_gates": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _P],
             "alofa_lru_scan": [_P, _P, _P, _P, _I, _I, _I, _P, _L, _P, _P, _I, _I, _I, _I, _P],
         }
         for name, args in sigs.items():
@@ -1276,22 +1276,28 @@ def _gated_lru():
     return lib
 
 
-def lru_gates(a, b, u, wa_t, wi_t, ba, bi, rate, blocks: int) -> None:
+def lru_gates(a, b, u, wa_t, wi_t, ba, bi, lam, decay_scale: float, blocks: int, wa_rows=None, wi_rows=None) -> None:
     """Decays and driven inputs of the gated linear recurrent unit, all fp32:
     per block of ``W / blocks`` channels ``r = sigmoid(A u_b + ba)``, ``i =
-    sigmoid(I u_b + bi)``; ``a = exp(rate * r)`` (``rate`` [W], not positive)
-    and ``b = sqrt(1 - a^2) * i * u``.  u, a, b [T, W]; ``wa_t``, ``wi_t``
-    [blocks, in, out]: the blocks' matrices transposed."""
+    sigmoid(I u_b + bi)``; ``a = exp(-decay_scale * r * softplus(lam))`` (``lam``
+    [W]) and ``b = sqrt(1 - a^2) * i * u``.  u, a, b [T, W]; ``wa_t``, ``wi_t``
+    [blocks, in, out]: the blocks' matrices transposed; ``wa_rows``, ``wi_rows``
+    (optional): the same as [blocks, out, in], which steps of a few tokens read
+    with a warp per output channel."""
     f32 = torch.float32
     n, width = u.shape
     if width % blocks:
         raise AlofaError("invalid_argument", "the blocks must divide the recurrence's width", f"width={width} blocks={blocks}")
     bs = width // blocks
     if (tuple(a.shape) != (n, width) or tuple(b.shape) != (n, width) or tuple(wa_t.shape) != (blocks, bs, bs) or tuple(wi_t.shape) != (blocks, bs, bs)
-            or ba.shape[0] != width or bi.shape[0] != width or rate.shape[0] != width):
+            or ba.shape[0] != width or bi.shape[0] != width or lam.shape[0] != width):
         raise AlofaError("invalid_argument", "lru_gates sizes disagree", f"u={tuple(u.shape)} wa={tuple(wa_t.shape)} blocks={blocks}")
-    _done(_gated_lru().alofa_lru_gates(_dev(a, "a", f32), _dev(b, "b", f32), _dev(u, "u", f32), _dev(wa_t, "wa", f32), _dev(wi_t, "wi", f32), _dev(ba, "ba", f32),
-                                       _dev(bi, "bi", f32), _dev(rate, "rate", f32), n, width, blocks, _stream()), "lru_gates", f"width={width} blocks={blocks}")
+    rows = wa_rows is not None and wi_rows is not None
+    if rows and (tuple(wa_rows.shape) != (blocks, bs, bs) or tuple(wi_rows.shape) != (blocks, bs, bs)):
+        raise AlofaError("invalid_argument", "lru_gates sizes disagree", f"wa_rows={tuple(wa_rows.shape)} blocks={blocks}")
+    _done(_gated_lru().alofa_lru_gates(_dev(a, "a", f32), _dev(b, "b", f32), _dev(u, "u", f32), _dev(wa_t, "wa", f32), _dev(wi_t, "wi", f32),
+                                       _dev(wa_rows, "wa_rows", f32) if rows else None, _dev(wi_rows, "wi_rows", f32) if rows else None, _dev(ba, "ba", f32),
+                                       _dev(bi, "bi", f32), _dev(lam, "lam", f32), float(decay_scale), n, width, blocks, _stream()), "lru_gates", f"width={width} blocks={blocks}")
 
 
 def lru_scan(out, a, b, y, y_off: int, act: str, state, q_start, state_slots, n_seqs: int) -> None:

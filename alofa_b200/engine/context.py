@@ -126,6 +126,10 @@ class StepContext:
         # sublayer left owed, (y, out weights, mix weights), which the next reader of the streams does
         self.streams = None
         self.streams_owed = None
+        # (h, rows, layer): the stream's rows in the compute dtype as the kernel that last added to the stream left them, and the
+        # number of the layer that did; a block whose first sublayer reads the stream itself takes them if it is the very next layer
+        self.stream_rows = None
+        self.layer_no = 0
 
     # -- the residual stream ---------------------------------------------------------------------
     # A product that adds into the stream may leave its split sums for the next reader to add
@@ -263,6 +267,7 @@ class StepContext:
     def begin_layer(self) -> None:
         """The model calls this before each entry of its run list."""
         self.arena.begin_layer()
+        self.layer_no += 1
 
     def end_layers(self) -> None:
         self.arena.end_layers()

@@ -194,21 +194,25 @@ class PostnormResidual(Part):
         wide = self.rt.dtype == torch.float32
         x = h  # the 32-bit path reads the stream in place: a sublayer is done with it before the norm's kernel adds to it
         if not wide:
-            x = ctx.buf(tuple(h.shape), self.rt.dtype)
-            ops.cast_rows(x, h)
+            left, ctx.stream_rows = ctx.stream_rows, None
+            if left is not None and left[0] is h and left[2] == ctx.layer_no - 1:
+                x = left[1]  # the layer before this one left the rows with its last norm
+            else:
+                x = ctx.buf(tuple(h.shape), self.rt.dtype)
+                ops.cast_rows(x, h)
         y = ctx.buf(tuple(h.shape), torch.float32)
         self.mixer.forward(ctx, x, y, cache, writes, store=True)
-        if self.feed_forward is None:
-            ops.sandwich_norm(h, y, self.mixer_post.weight, self.mixer_post.eps)
-            return
-        if wide:
-            ops.sandwich_norm(h, y, self.mixer_post.weight, self.mixer_post.eps)
-        else:
-            x = ctx.buf(tuple(h.shape), self.rt.dtype)
+        if self.feed_forward is not None:
+            x = None if wide else ctx.buf(tuple(h.shape), self.rt.dtype)
             ops.sandwich_norm(h, y, self.mixer_post.weight, self.mixer_post.eps, x)
-        y = ctx.buf(tuple(h.shape), torch.float32)
-        self.feed_forward.forward(ctx, x, y, store=True)
-        ops.sandwich_norm(h, y, self.feed_forward_post.weight, self.feed_forward_post.eps)
+            y = ctx.buf(tuple(h.shape), torch.float32)
+            self.feed_forward.forward(ctx, h if wide else x, y, store=True)
+        last = self.feed_forward_post if self.feed_forward is not None else self.mixer_post
+        # the layer's last norm also leaves the rows that the next layer's mixer reads (a scratch buffer of a layer lives until the layer after next begins)
+        x = None if wide else ctx.buf(tuple(h.shape), self.rt.dtype)
+        ops.sandwich_norm(h, y, last.weight, last.eps, x)
+        if x is not None:
+            ctx.stream_rows = (h, x, ctx.layer_no)
 
 
 class EmbeddingMixIn(Part):

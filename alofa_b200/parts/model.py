@@ -66,6 +66,7 @@ class Model:
         """Logits (fp32) at ``ctx.logit_rows`` for the step's tokens (None when
         no row is wanted; the final norm and the head run on wanted rows only)."""
         h = ctx.buf((ctx.n_tokens, self.spec.hidden_size), torch.float32)
+        ctx.stream_rows = None  # nothing is left over from another pass over the layers
         ctx.open_stream(h)
         self.embedding.forward(ctx, h)
         if self.keeps_embedding:

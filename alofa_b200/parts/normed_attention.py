@@ -103,7 +103,8 @@ class NormedAttention(PagedAttend, Part):
 
     def cache_spec(self):
         # a chunk never reaches further back than its own size: the pages behind it are given back like a window's
-        return PagedKV(self.kv_heads * self.maps, self.dim, self.chunk or self.window, self.vdim, self.kv_heads * self.v_copies)
+        value_heads = self.kv_heads * self.v_copies
+        return PagedKV(self.kv_heads * self.maps, self.dim, self.chunk or self.window, self.vdim, None if value_heads == self.kv_heads * self.maps else value_heads)
 
     def scratch_row_bytes(self) -> int:
         return 4 * self.rows + 4 * self.q_dim + 4 * (self.maps + 1) * self.heads * self.vdim + 8 * self.hidden

@@ -368,11 +368,11 @@ class GatedLRU(Part):
         self.conv_w = state[pre + "conv"].to(f32).contiguous()
         self.conv_b = as_float32_vector(state[pre + "conv.b"])
         # the gates are part of the recurrence: fp32 whatever the compute dtype, [block][in][out] for the kernel
-        self.wa_t = state[pre + "ra"].to(f32).transpose(1, 2).contiguous()
-        self.wi_t = state[pre + "ri"].to(f32).transpose(1, 2).contiguous()
+        self.wa_rows, self.wi_rows = state[pre + "ra"].to(f32).contiguous(), state[pre + "ri"].to(f32).contiguous()  # as stored, for steps of a few tokens
+        self.wa_t, self.wi_t = self.wa_rows.transpose(1, 2).contiguous(), self.wi_rows.transpose(1, 2).contiguous()
         self.ba = as_float32_vector(state[pre + "ra.b"].reshape(-1))
         self.bi = as_float32_vector(state[pre + "ri.b"].reshape(-1))
-        self.rate = (-self.decay_scale * torch.nn.functional.softplus(state[pre + "lam"].to(f32))).contiguous()  # log a = rate * r
+        self.lam = as_float32_vector(state[pre + "lam"])
         self.out_add = Linear(state[pre + "o"], None, RESIDUAL)
         self.out_store = Linear(state[pre + "o"], None, STORE)
 
@@ -384,7 +384,7 @@ class GatedLRU(Part):
         xc = ctx.buf((n, w), f32)
         ops.causal_conv(xc, u, w, self.conv_w, self.conv_b, st[:, w:], ctx.q_start, ctx.state_slots, ctx.seq_of_token, ctx.n_seqs, act=False)
         a, b = ctx.buf((n, w), f32), ctx.buf((n, w), f32)
-        ops.lru_gates(a, b, xc, self.wa_t, self.wi_t, self.ba, self.bi, self.rate, self.blocks)
+        ops.lru_gates(a, b, xc, self.wa_t, self.wi_t, self.ba, self.bi, self.lam, self.decay_scale, self.blocks, self.wa_rows, self.wi_rows)
         y = ctx.buf((n, w), self.rt.dtype)
         ops.lru_scan(y, a, b, u, 0, self.act, st, ctx.q_start, ctx.state_slots, ctx.n_seqs)
         _project_out(ctx, self.out_add, self.out_store, h, y, store)

@@ -51,7 +51,7 @@ def test_the_description_names_the_tensors_parts_and_caches(folders, name):
         if layer["type"] == "parallel":
             a, r = m["left"], m["right"]
             # keys and values of the same size (the values are the keys before their norm), every key kept; the state, then the convolution's last inputs
-            assert plan[i] == (PagedKV(a["kv_heads"], a["dim"], None, a["dim"], a["kv_heads"]), SlotState((r["width"] * r["conv"],)))
+            assert plan[i] == (PagedKV(a["kv_heads"], a["dim"], None, a["dim"]), SlotState((r["width"] * r["conv"],)))
         else:
             # two keys a key head, one value; a chunk's pages are given back like a window's
             assert plan[i] == PagedKV(2 * m["kv_heads"], m["dim"], m.get("mask", {}).get("size"), m["vdim"], m["kv_heads"])

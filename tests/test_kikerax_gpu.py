@@ -299,8 +299,9 @@ class Unit:
         self.bias = np.concatenate([w["r.y.b"], w["r.x.b"]])
         self.conv_w, self.conv_b = dev(w["r.conv"], F32), dev(w["r.conv.b"], F32)
         self.wa, self.wi = dev(np.transpose(w["r.ra"], (0, 2, 1)), F32), dev(np.transpose(w["r.ri"], (0, 2, 1)), F32)
+        self.wa_rows, self.wi_rows = dev(w["r.ra"], F32), dev(w["r.ri"], F32)
         self.ba, self.bi = dev(w["r.ra.b"].reshape(-1), F32), dev(w["r.ri.b"].reshape(-1), F32)
-        self.rate = dev(-8.0 * np.log1p(np.exp(w["r.lam"])), F32)
+        self.lam = dev(w["r.lam"], F32)
 
     def step(self, x, q_start, slots, seq, n_seqs):
         from alofa_b200.csrc import ops
@@ -310,7 +311,7 @@ class Unit:
         xc = torch.empty((n, W), dtype=F32, device="cuda")
         ops.causal_conv(xc, u, W, self.conv_w, self.conv_b, self.state[:, W:], q_start, slots, seq, n_seqs, act=False)
         a, b = torch.empty_like(xc), torch.empty_like(xc)
-        ops.lru_gates(a, b, xc, self.wa, self.wi, self.ba, self.bi, self.rate, self.B)
+        ops.lru_gates(a, b, xc, self.wa, self.wi, self.ba, self.bi, self.lam, 8.0, self.B, self.wa_rows, self.wi_rows)
         y = torch.empty((n, W), dtype=self.dtype, device="cuda")
         ops.lru_scan(y, a, b, u, 0, "gelu_tanh", self.state, q_start, slots, n_seqs)
         return y.float().cpu().numpy()
