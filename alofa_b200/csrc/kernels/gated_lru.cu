@@ -90,7 +90,8 @@ __global__ void __launch_bounds__(LRU_OT) lru_gates_kernel(float* __restrict__ a
 // thread waiting for its own weights: wa_rows, wi_rows [B][out][in] as the checkpoint has them; a warp takes an output
 // channel at a time, its lanes share the block's inputs four neighbours each (16-byte loads of the weights' rows), and
 // the lanes' shares are added in butterfly order.  The order of a sum's additions depends on the block's size alone.
-constexpr int LRU_ROWS_OUT = 32;  // outputs a CTA of eight warps takes
+constexpr int LRU_ROWS_OUT = 8;  // outputs a CTA of eight warps takes: one a warp, so that a decode step's few tokens still spread over every SM
+                                 // (with 32, eight tokens of 1,280 channels ran on 40 blocks, each warp waiting for its weights four times in turn: 23 us cold)
 
 __global__ void __launch_bounds__(256) lru_gates_rows_kernel(float* __restrict__ a_out, float* __restrict__ b_out, const float* __restrict__ u,
                                                              const float* __restrict__ wa, const float* __restrict__ wi, const float* __restrict__ ba,

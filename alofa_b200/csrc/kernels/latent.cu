@@ -429,20 +429,54 @@ ALOFA_API int alofa_latent_attention(void* out, const void* qa, const void* cach
 // sublayer; without w_next the updated row itself) in the compute dtype.  One
 // block per row, fp32 throughout.
 // ---------------------------------------------------------------------------
+// y may still be owed: `splits` planes of partial sums (plane z at y + z * plane) that a product left for this kernel
+// to add, in split order, and a bias on top - the same additions in the same order as the kernel that would
+// otherwise have added them up.  splits 0: y is the finished output.
+struct OwedSums {
+  int splits;
+  long long plane;
+  const float* bias;
+};
+
+__device__ __forceinline__ float owed_value(const float* __restrict__ y, const OwedSums& o, size_t at, int c) {
+  if (o.splits == 0) return y[at];
+  float a = 0.f;
+  for (int z = 0; z < o.splits; ++z) a += y[(size_t)z * o.plane + at];
+  if (o.bias) a += o.bias[c];
+  return a;
+}
+
+__device__ __forceinline__ float4 owed_value4(const float* __restrict__ y, const OwedSums& o, size_t at, int c) {
+  if (o.splits == 0) return *reinterpret_cast<const float4*>(y + at);
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int z = 0; z < o.splits; ++z) {
+    const float4 v = *reinterpret_cast<const float4*>(y + (size_t)z * o.plane + at);
+    a.x += v.x, a.y += v.y, a.z += v.z, a.w += v.w;
+  }
+  if (o.bias) {
+    const float4 b = *reinterpret_cast<const float4*>(o.bias + c);
+    a.x += b.x, a.y += b.y, a.z += b.z, a.w += b.w;
+  }
+  return a;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) sandwich_norm_kernel(float* __restrict__ h, const float* __restrict__ y, const float* __restrict__ w_post,
                                                             float eps_post, T* __restrict__ x, const float* __restrict__ w_next, float eps_next,
-                                                            int hidden) {
+                                                            int hidden, OwedSums owed) {
   __shared__ float scratch[32];
   pdl_begin();
   const size_t r = (size_t)blockIdx.x * hidden;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) ss = fmaf(y[r + c], y[r + c], ss);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float v = owed_value(y, owed, r + c, c);
+    ss = fmaf(v, v, ss);
+  }
   ss = block_sum(ss, scratch);
   const float f = 1.0f / sqrtf(ss / (float)hidden + eps_post);
   float s2 = 0.f;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-    const float v = h[r + c] + y[r + c] * f * w_post[c];
+    const float v = h[r + c] + owed_value(y, owed, r + c, c) * f * w_post[c];
     h[r + c] = v;
     s2 = fmaf(v, v, s2);
   }
@@ -463,7 +497,7 @@ __global__ void __launch_bounds__(256) sandwich_norm_kernel(float* __restrict__ 
 template <typename T, int CHUNKS>
 __global__ void __launch_bounds__(256) sandwich_norm_rows_kernel(float* __restrict__ h, const float* __restrict__ y, const float* __restrict__ w_post,
                                                                  float eps_post, T* __restrict__ x, const float* __restrict__ w_next, float eps_next,
-                                                                 int hidden) {
+                                                                 int hidden, OwedSums owed) {
   __shared__ float scratch[32];
   pdl_begin();
   const size_t r = (size_t)blockIdx.x * hidden;
@@ -474,7 +508,7 @@ __global__ void __launch_bounds__(256) sandwich_norm_rows_kernel(float* __restri
   for (int i = 0; i < CHUNKS; ++i) {
     const int c = threadIdx.x + 256 * i;
     if (c < quads) {
-      yv[i] = reinterpret_cast<const float4*>(y + r)[c];
+      yv[i] = owed_value4(y, owed, r + 4 * (size_t)c, 4 * c);
       hv[i] = reinterpret_cast<const float4*>(h + r)[c];
       ss = fmaf(yv[i].x, yv[i].x, fmaf(yv[i].y, yv[i].y, fmaf(yv[i].z, yv[i].z, fmaf(yv[i].w, yv[i].w, ss))));
     }
@@ -514,21 +548,28 @@ __global__ void __launch_bounds__(256) sandwich_norm_rows_kernel(float* __restri
 
 template <typename T>
 static void sandwich_norm_launch(float* h, const float* y, const float* w_post, float eps_post, T* x, const float* w_next, float eps_next, int rows,
-                                 int hidden, cudaStream_t stream) {
-  const bool aligned = (hidden & 3) == 0 && !(((uintptr_t)h | (uintptr_t)y | (uintptr_t)w_post | (uintptr_t)w_next) & 15);
+                                 int hidden, OwedSums owed, cudaStream_t stream) {
+  const bool aligned = (hidden & 3) == 0 && !(((uintptr_t)h | (uintptr_t)y | (uintptr_t)w_post | (uintptr_t)w_next | (uintptr_t)owed.bias) & 15) && (owed.plane & 3) == 0;
   if (aligned && hidden <= 4 * 256 * 2)
-    launch_dep(sandwich_norm_rows_kernel<T, 2>, rows, 256, 0, stream, h, y, w_post, eps_post, x, w_next, eps_next, hidden);
+    launch_dep(sandwich_norm_rows_kernel<T, 2>, rows, 256, 0, stream, h, y, w_post, eps_post, x, w_next, eps_next, hidden, owed);
   else if (aligned && hidden <= 4 * 256 * 8)
-    launch_dep(sandwich_norm_rows_kernel<T, 8>, rows, 256, 0, stream, h, y, w_post, eps_post, x, w_next, eps_next, hidden);
+    launch_dep(sandwich_norm_rows_kernel<T, 8>, rows, 256, 0, stream, h, y, w_post, eps_post, x, w_next, eps_next, hidden, owed);
   else
-    launch_dep(sandwich_norm_kernel<T>, rows, 256, 0, stream, h, y, w_post, eps_post, x, w_next, eps_next, hidden);
+    launch_dep(sandwich_norm_kernel<T>, rows, 256, 0, stream, h, y, w_post, eps_post, x, w_next, eps_next, hidden, owed);
 }
 
+// splits > 0: y holds that many planes of partial sums [rows, hidden] (plane z at y + z * plane floats) still to be added
+// up, with y_bias (may be null) on top; splits 0: y is the sublayer's finished output.
 ALOFA_API int alofa_sandwich_norm(float* h, const float* y, const float* w_post, float eps_post, void* x, const float* w_next, float eps_next,
-                                  int rows, int hidden, int x_bf16, cudaStream_t stream) {
+                                  int rows, int hidden, int x_bf16, int splits, long long plane, const float* y_bias, cudaStream_t stream) {
   if (rows <= 0) return ALOFA_OK;
-  if (x_bf16) sandwich_norm_launch<bf16>(h, y, w_post, eps_post, (bf16*)x, w_next, eps_next, rows, hidden, stream);
-  else sandwich_norm_launch<float>(h, y, w_post, eps_post, (float*)x, w_next, eps_next, rows, hidden, stream);
+  if (splits < 0 || (splits > 0 && plane < (long long)rows * hidden)) return ALOFA_ERR_ARGUMENT;
+  OwedSums owed;
+  owed.splits = splits;
+  owed.plane = plane;
+  owed.bias = splits > 0 ? y_bias : nullptr;
+  if (x_bf16) sandwich_norm_launch<bf16>(h, y, w_post, eps_post, (bf16*)x, w_next, eps_next, rows, hidden, owed, stream);
+  else sandwich_norm_launch<float>(h, y, w_post, eps_post, (float*)x, w_next, eps_next, rows, hidden, owed, stream);
   return launch_status();
 }
 

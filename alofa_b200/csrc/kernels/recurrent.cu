@@ -484,21 +484,35 @@ template <typename T>
 __global__ void __launch_bounds__(256) qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const float* __restrict__ qkv, int ld,
                                                           const int* __restrict__ positions, const int* __restrict__ slot_map, int H, int G, int d, int dv, int maps,
                                                           int qk_norm, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps, float coef, int every,
-                                                          int n_tokens, const float* __restrict__ freq, int rot_dims, float mag, int v_from_k, int v_copies) {
+                                                          int n_tokens, const float* __restrict__ freq, int rot_dims, float mag, int v_from_k, int v_copies,
+                                                          int splits, long long plane, const float* __restrict__ bias, float* __restrict__ extra_out, int extra_at,
+                                                          int extra_n) {
   pdl_begin();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int HQ = H * maps, GK = G * maps;
-  const int per = HQ + GK + G;
+  const int per = HQ + GK + G + (extra_out ? 1 : 0);
   const long long unit = (long long)blockIdx.x * 8 + warp;
   if (unit >= (long long)n_tokens * per) return;
   const int t = (int)(unit / per), u = (int)(unit - (long long)t * per);
   const float* row = qkv + (size_t)t * ld;
+  // column `col` of the token's row: the finished sum, or (splits > 0) the planes of partial sums a product left owed,
+  // added in split order with the bias on top, as the kernel that settles them would have
+  auto at = [&](int col) -> float {
+    if (splits == 0) return row[col];
+    float a = 0.f;
+    for (int z = 0; z < splits; ++z) a += row[(size_t)z * plane + col];
+    if (bias) a += bias[col];
+    return a;
+  };
   if (u < HQ + GK) {
-    const float* x = row + (size_t)u * d;
+    const int x0 = u * d;  // the unit's first column
     float mul = 1.f;
     if (qk_norm) {
       float ss = 0.f;
-      for (int c = lane; c < d; c += 32) ss = fmaf(x[c], x[c], ss);
+      for (int c = lane; c < d; c += 32) {
+        const float v = at(x0 + c);
+        ss = fmaf(v, v, ss);
+      }
       ss = warp_sum(ss);
       mul = 1.0f / sqrtf(ss / (float)d + eps);
     }
@@ -524,42 +538,50 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(T* __restrict__ q_out,
         sincosf(p * freq[i], &sn, &cs);
         sn *= mag;
         cs *= mag;
-        float a = x[2 * i] * mul, b = x[2 * i + 1] * mul;
+        float a = at(x0 + 2 * i) * mul, b = at(x0 + 2 * i + 1) * mul;
         if (w) a *= w[2 * i], b *= w[2 * i + 1];
         to[2 * i] = from_f<T>(a * cs - b * sn);
         to[2 * i + 1] = from_f<T>(b * cs + a * sn);
       }
     }
-    if (w) for (int c = rot_dims + lane; c < d; c += 32) to[c] = from_f<T>(x[c] * mul * w[c]);
-    else for (int c = rot_dims + lane; c < d; c += 32) to[c] = from_f<T>(x[c] * mul);
-  } else {
+    if (w) for (int c = rot_dims + lane; c < d; c += 32) to[c] = from_f<T>(at(x0 + c) * mul * w[c]);
+    else for (int c = rot_dims + lane; c < d; c += 32) to[c] = from_f<T>(at(x0 + c) * mul);
+  } else if (u < HQ + GK + G) {
     const int gi = u - HQ - GK;
     // the values: their own columns, or (v_from_k) the keys as projected, before their norm
-    const float* x = v_from_k ? row + (size_t)HQ * d + (size_t)gi * d : row + (size_t)(HQ + GK) * d + (size_t)gi * dv;
+    const int x0 = v_from_k ? HQ * d + gi * d : (HQ + GK) * d + gi * dv;
     // v_copies > 1: the value head is written that many times side by side, one for each of the key head's keys
     T* to = v_cache + ((size_t)slot_map[t] * G + gi) * v_copies * dv;
     for (int c = lane; c < dv; c += 32) {
-      const T v = from_f<T>(x[c]);
+      const T v = from_f<T>(at(x0 + c));
       for (int k = 0; k < v_copies; ++k) to[(size_t)k * dv + c] = v;
     }
+  } else {
+    // what follows q, k and v in the row (a gate's logits): finished, for the kernels after the attention
+    for (int c = lane; c < extra_n; c += 32) extra_out[(size_t)t * extra_n + c] = at(extra_at + c);
   }
 }
 
+// splits > 0: qkv holds that many planes of partial sums (plane z at qkv + z * plane floats) still to be added up, with bias
+// (may be null) on top.  extra_out (may be null): the extra_n columns from extra_at on are written there, finished, [T, extra_n].
 ALOFA_API int alofa_qkv_prepare(void* q_out, void* k_cache, void* v_cache, const float* qkv, int ld, const int* positions, const int* slot_map, int n_tokens, int H, int G,
                                 int d, int dv, int maps, int qk_norm, const float* q_w, const float* k_w, float eps, float coef, int every, const float* freq,
-                                int rot_dims, float mag, int v_from_k, int v_copies, int is_bf16, cudaStream_t stream) {
+                                int rot_dims, float mag, int v_from_k, int v_copies, int is_bf16, int splits, long long plane, const float* bias, float* extra_out,
+                                int extra_at, int extra_n, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
   if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || maps <= 0 || (coef != 0.f && every <= 0) || rot_dims < 0 || rot_dims > d || (rot_dims & 1) || (rot_dims && !freq) ||
-      (v_from_k && (maps != 1 || dv != d)) || v_copies < 1 || ld < (H + G) * maps * d + (v_from_k ? 0 : G * dv))
+      (v_from_k && (maps != 1 || dv != d)) || v_copies < 1 || ld < (H + G) * maps * d + (v_from_k ? 0 : G * dv) || splits < 0 ||
+      (splits > 0 && plane < (long long)n_tokens * ld) || (extra_out && (extra_n <= 0 || extra_at < 0 || extra_at + extra_n > ld)))
     return ALOFA_ERR_ARGUMENT;
-  const long long units = (long long)n_tokens * ((H + G) * maps + G);
+  if (splits == 0) bias = nullptr;
+  const long long units = (long long)n_tokens * ((H + G) * maps + G + (extra_out ? 1 : 0));
   const unsigned blocks = (unsigned)((units + 7) / 8);
   if (is_bf16)
     launch_dep(qkv_prepare_kernel<bf16>, blocks, 256, 0, stream, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, qkv, ld, positions, slot_map, H, G, d, dv, maps, qk_norm,
-               q_w, k_w, eps, coef, every, n_tokens, freq, rot_dims, mag, v_from_k, v_copies);
+               q_w, k_w, eps, coef, every, n_tokens, freq, rot_dims, mag, v_from_k, v_copies, splits, plane, bias, extra_out, extra_at, extra_n);
   else
     launch_dep(qkv_prepare_kernel<float>, blocks, 256, 0, stream, (float*)q_out, (float*)k_cache, (float*)v_cache, qkv, ld, positions, slot_map, H, G, d, dv, maps,
-               qk_norm, q_w, k_w, eps, coef, every, n_tokens, freq, rot_dims, mag, v_from_k, v_copies);
+               qk_norm, q_w, k_w, eps, coef, every, n_tokens, freq, rot_dims, mag, v_from_k, v_copies, splits, plane, bias, extra_out, extra_at, extra_n);
   return launch_status();
 }
 

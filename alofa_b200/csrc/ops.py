@@ -490,9 +490,11 @@ def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, positions, block_t
         count_launches(1)
 
 
-def attention_combine(out, partial_o, partial_ml, positions, nh: int, hd: int, window, split_keys: int, sink=None) -> None:
-    """Merge the key splits of decode tokens: out [T, nh * hd] bf16."""
-    rc = _attention(hd).alofa_attention_combine(
+def attention_combine(out, partial_o, partial_ml, positions, nh: int, hd: int, window, split_keys: int, sink=None, capped: bool = False) -> None:
+    """Merge the key splits of decode tokens: out [T, nh * hd] bf16.  ``capped``:
+    take the kernel from the library built for capped scores (the one the
+    splits came from), so that no second library is built for it."""
+    rc = _attention(hd, capped).alofa_attention_combine(
         _dev(out, "out", torch.bfloat16), _dev(partial_o, "partial_o", torch.float32), _dev(partial_ml, "partial_ml", torch.float32),
         _dev(positions, "positions", torch.int32), out.shape[0], nh, int(window or 0), split_keys,
         _dev(sink, "sink", torch.float32) if sink is not None else None, _stream(),
@@ -581,7 +583,7 @@ def _latent():
             "alofa_gemm_batched_bf16": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _I, _I, _I, _P],
             "alofa_activate": [_P, _P, _P, _L, _I, _I, _I, _P],
             "alofa_latent_attention": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
-            "alofa_sandwich_norm": [_P, _P, _P, _F, _P, _P, _F, _I, _I, _I, _P],
+            "alofa_sandwich_norm": [_P, _P, _P, _F, _P, _P, _F, _I, _I, _I, _I, _L, _P, _P],
             "alofa_concat_rows": [_P, _P, _P, _I, _I, _I, _P],
             "alofa_moe_route": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
             "alofa_moe_router": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _F, _I, _I, _F, _P],
@@ -721,14 +723,26 @@ def latent_attention(out, qa, cache_rows, sink, positions, seq_of_token, block_t
 def sandwich_norm(h, y, w_post, eps_post: float, x=None, w_next=None, eps_next: float = 0.0) -> None:
     """``h += rmsnorm(y) * w_post`` (fp32 stream); with ``x`` also ``x =
     rmsnorm(h) * w_next`` of the updated rows (without ``w_next``: the updated
-    rows themselves), in x's dtype."""
+    rows themselves), in x's dtype.  ``y`` is the sublayer's output [rows,
+    hidden] fp32, or the partial sums a product left owed (``.sums`` [splits,
+    rows, hidden], ``.splits``, ``.bias``): they are added here, in split
+    order, as the kernel that settles them would have."""
     rows, hidden = h.shape
-    if tuple(y.shape) != (rows, hidden) or (x is not None and tuple(x.shape) != (rows, hidden)):
-        raise AlofaError("invalid_argument", "sandwich_norm sizes disagree", f"h={tuple(h.shape)} y={tuple(y.shape)}")
     f32 = torch.float32
+    splits, plane, bias = 0, 0, None
+    if not isinstance(y, torch.Tensor):
+        splits, bias, y = int(y.splits), y.bias, y.sums
+        if tuple(y.shape) != (splits, rows, hidden):
+            raise AlofaError("invalid_argument", "sandwich_norm: owed sums disagree with the stream", f"h={tuple(h.shape)} sums={tuple(y.shape)}")
+        plane = rows * hidden
+    elif tuple(y.shape) != (rows, hidden):
+        raise AlofaError("invalid_argument", "sandwich_norm sizes disagree", f"h={tuple(h.shape)} y={tuple(y.shape)}")
+    if x is not None and tuple(x.shape) != (rows, hidden):
+        raise AlofaError("invalid_argument", "sandwich_norm sizes disagree", f"h={tuple(h.shape)} x={tuple(x.shape)}")
     _done(
         _latent().alofa_sandwich_norm(_dev(h, "h", f32), _dev(y, "y", f32), _dev(w_post, "w_post", f32), float(eps_post), _dev(x, "x") if x is not None else None,
-                                      _dev(w_next, "w_next", f32) if x is not None and w_next is not None else None, float(eps_next), rows, hidden, _is_bf16(x, "x") if x is not None else 0, _stream()),
+                                      _dev(w_next, "w_next", f32) if x is not None and w_next is not None else None, float(eps_next), rows, hidden,
+                                      _is_bf16(x, "x") if x is not None else 0, splits, plane, _dev(bias, "bias", f32) if bias is not None else None, _stream()),
         "sandwich_norm",
     )
 
@@ -917,7 +931,7 @@ def _recurrent():
             "alofa_linear_scan": [_P, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _F, _F, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
             "alofa_gated_group_norm": [_P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P],
             "alofa_branch_norm_add": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _P],
-            "alofa_qkv_prepare": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _F, _I, _P, _I, _F, _I, _I, _I, _P],
+            "alofa_qkv_prepare": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _F, _I, _P, _I, _F, _I, _I, _I, _I, _L, _P, _P, _I, _I, _P],
             "alofa_heads_finish": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _I, _I, _P],
         }
         for name, args in sigs.items():
@@ -1052,7 +1066,7 @@ def branch_norm_add(h, ya, wa, yb, wb, eps: float, scale: float) -> None:
 
 
 def qkv_prepare(q_out, k_cache, v_cache, qkv, positions, slot_map, heads: int, kv_heads: int, d: int, dv: int, qk_norm: bool, eps: float, coef: float, every: int,
-                freq=None, rot_dims: int = 0, maps: int = 1, q_weight=None, k_weight=None, magnitude: float = 1.0, values_from_keys: bool = False, v_copies: int = 1) -> None:
+                freq=None, rot_dims: int = 0, maps: int = 1, q_weight=None, k_weight=None, magnitude: float = 1.0, values_from_keys: bool = False, v_copies: int = 1, extra_out=None, extra_at: int = 0) -> None:
     """From the fp32 sums of a stacked projection whose rows start [q | k | v]
     (more columns may follow): q and k divided by their root mean square per
     head (``qk_norm``) and multiplied by ``q_weight`` / ``k_weight`` (fp32
@@ -1068,10 +1082,23 @@ def qkv_prepare(q_out, k_cache, v_cache, qkv, positions, slot_map, heads: int, k
     no v columns, the values are the keys as projected (before their norm).
     ``v_copies`` > 1: every value head is written that many times side by side
     (the value cache then has ``kv_heads * v_copies`` heads), for kernels that
-    want a value head for each key head."""
+    want a value head for each key head.  ``qkv`` may be the partial sums a
+    product left owed (``.sums`` [splits, T, ld], ``.splits``, ``.bias``): they
+    are added here, in split order.  ``extra_out`` (fp32 [T, m]): the m columns
+    from ``extra_at`` on (what follows q, k and v in the row) are written there,
+    finished."""
+    f32 = torch.float32
+    splits, plane, bias = 0, 0, None
+    if not isinstance(qkv, torch.Tensor):
+        splits, bias, sums = int(qkv.splits), qkv.bias, qkv.sums
+        qkv = sums[0]
+        plane = sums.shape[1] * sums.shape[2]
+        if sums.shape[0] != splits or not sums.is_contiguous():
+            raise AlofaError("invalid_argument", "qkv_prepare: owed sums disagree with their count", f"sums={tuple(sums.shape)} splits={splits}")
     n = qkv.shape[0]
     dt = q_out.dtype
-    f32 = torch.float32
+    if extra_out is not None and (extra_out.shape[0] != n or extra_at + extra_out.shape[1] > qkv.shape[1]):
+        raise AlofaError("invalid_argument", "qkv_prepare: the extra columns lie outside the row", f"qkv={tuple(qkv.shape)} extra={tuple(extra_out.shape)} at={extra_at}")
     need = (heads + kv_heads) * maps * d + (0 if values_from_keys else kv_heads * dv)
     if (qkv.shape[1] < need or tuple(q_out.shape) != (n, heads * maps * d) or tuple(k_cache.shape[1:]) != (kv_heads * maps, d) or tuple(v_cache.shape[1:]) != (kv_heads * v_copies, dv)
             or (q_weight is not None and q_weight.shape[0] != d) or (k_weight is not None and k_weight.shape[0] != d)):
@@ -1082,7 +1109,9 @@ def qkv_prepare(q_out, k_cache, v_cache, qkv, positions, slot_map, heads: int, k
                                        1 if qk_norm else 0, _dev(q_weight, "q_weight", f32) if q_weight is not None else None,
                                        _dev(k_weight, "k_weight", f32) if k_weight is not None else None, float(eps), float(coef), int(every),
                                        _dev(freq, "freq", f32) if rot_dims else None, int(rot_dims), float(magnitude), 1 if values_from_keys else 0, int(v_copies),
-                                       _is_bf16(q_out, "q_out"), _stream()),
+                                       _is_bf16(q_out, "q_out"), splits, plane, _dev(bias, "bias", f32) if bias is not None else None,
+                                       _dev(extra_out, "extra_out", f32) if extra_out is not None else None, int(extra_at),
+                                       extra_out.shape[1] if extra_out is not None else 0, _stream()),
         "qkv_prepare", f"heads={heads} kv_heads={kv_heads} d={d} dv={dv} maps={maps}",
     )
 

@@ -122,7 +122,7 @@ class PagedAttend:
                 sink=self.sink,
             )
             if unmerged:
-                return MergedSplits(po, pml, ctx.positions, ctx.n_tokens, self.nh, self.hd, self.window, per_split, ctx.buf)
+                return MergedSplits(po, pml, ctx.positions, ctx.n_tokens, self.nh, self.hd, self.window, per_split, ctx.buf, capped=self.softcap > 0)
             return out
         ops.paged_attention_generic(
             out, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size,

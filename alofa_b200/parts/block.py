@@ -189,6 +189,16 @@ class PostnormResidual(Part):
     def scratch_row_bytes(self) -> int:
         return 12 * self.mixer_post.size + sum(getattr(part, "scratch_row_bytes", lambda: 0)() for part in self.parts())
 
+    @staticmethod
+    def _output(ctx, part, h, x, *args):
+        """The sublayer's output for the rows ``x``: an fp32 buffer, or the split sums its last product left for the norm's kernel to add."""
+        y = ctx.buf(tuple(h.shape), torch.float32)
+        if getattr(part, "defers_output", False) and x.shape[0] > 64:  # in steps of a few tokens the kernel that settles the sums first measured faster
+            owed = part.forward(ctx, x, y, *args, store=True, defer=True)
+            return y if owed is None else owed
+        part.forward(ctx, x, y, *args, store=True)
+        return y
+
     def forward(self, ctx, h, cache, writes=True):
         ctx.flush_pending()
         wide = self.rt.dtype == torch.float32
@@ -200,13 +210,11 @@ class PostnormResidual(Part):
             else:
                 x = ctx.buf(tuple(h.shape), self.rt.dtype)
                 ops.cast_rows(x, h)
-        y = ctx.buf(tuple(h.shape), torch.float32)
-        self.mixer.forward(ctx, x, y, cache, writes, store=True)
+        y = self._output(ctx, self.mixer, h, x, cache, writes)
         if self.feed_forward is not None:
             x = None if wide else ctx.buf(tuple(h.shape), self.rt.dtype)
             ops.sandwich_norm(h, y, self.mixer_post.weight, self.mixer_post.eps, x)
-            y = ctx.buf(tuple(h.shape), torch.float32)
-            self.feed_forward.forward(ctx, h if wide else x, y, store=True)
+            y = self._output(ctx, self.feed_forward, h, h if wide else x)
         last = self.feed_forward_post if self.feed_forward is not None else self.mixer_post
         # the layer's last norm also leaves the rows that the next layer's mixer reads (a scratch buffer of a layer lives until the layer after next begins)
         x = None if wide else ctx.buf(tuple(h.shape), self.rt.dtype)

@@ -61,6 +61,7 @@ class DenseMLP(Part):
     family = "feed_forward"
     graph_safe = True
     stores_output = True  # forward(..., store=True) writes its output instead of adding it
+    defers_output = True  # forward(..., store=True, defer=True) may hand back the down product's split sums instead of the finished output
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -96,12 +97,12 @@ class DenseMLP(Part):
     def scratch_row_bytes(self) -> int:
         return 4 * self.inter + 4 * self.hidden
 
-    def forward(self, ctx, x, h, store=False):
+    def forward(self, ctx, x, h, store=False, defer=False):
         n = x.shape[0]
         mid = ctx.buf((n, self.inter), self.rt.dtype)
         self.up(mid, x, buf=ctx.buf)  # bias and activation on the fp32 sums, in the product's epilogue
         if store:
-            self.down(h, mid, buf=ctx.buf)
+            return self.down(h, mid, defer=defer, buf=ctx.buf)  # None, or the split sums a caller that asked for them adds up itself
         else:
             y = ctx.buf((n, self.hidden), torch.float32)
             self.down(y, mid, buf=ctx.buf)

@@ -43,9 +43,10 @@ class MergedSplits:
 
     dtype = torch.bfloat16
 
-    def __init__(self, partial_o, partial_ml, positions, tokens: int, heads: int, head_dim: int, window, split_keys: int, buf):
+    def __init__(self, partial_o, partial_ml, positions, tokens: int, heads: int, head_dim: int, window, split_keys: int, buf, capped: bool = False):
         self.partial_o, self.partial_ml, self.positions = partial_o, partial_ml, positions
         self.buf = buf  # the step's scratch allocator
+        self.capped = capped  # the splits came from the library built for capped scores
         self.heads, self.head_dim, self.window, self.split_keys = heads, head_dim, window, split_keys
         self.shape = (tokens, heads * head_dim)
 
@@ -57,7 +58,7 @@ class MergedSplits:
 
     def rows(self) -> torch.Tensor:
         out = self.buf(self.shape, torch.bfloat16)
-        ops.attention_combine(out, self.partial_o, self.partial_ml, self.positions, self.heads, self.head_dim, self.window, self.split_keys)
+        ops.attention_combine(out, self.partial_o, self.partial_ml, self.positions, self.heads, self.head_dim, self.window, self.split_keys, capped=self.capped)
         return out
 
 

@@ -45,10 +45,14 @@ from .base import PagedKV, Part, TensorSpec, as_float32_vector, build_part, regi
 from .linear import RESIDUAL, STORE, Linear, add_into_stream
 
 
+DEFER_ABOVE = 64  # tokens in a step above which a product's split sums are left for its reader to add
+
+
 class NormedAttention(PagedAttend, Part):
     family = "mixer"
     graph_safe = True
     stores_output = True
+    defers_output = True  # forward(..., store=True, defer=True) may hand back its last product's split sums instead of the finished output
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -151,28 +155,34 @@ class NormedAttention(PagedAttend, Part):
         self.out_add = Linear(state[pre + "o"], ob, RESIDUAL)
         self.out_store = Linear(state[pre + "o"], ob, STORE)
 
-    def forward(self, ctx, x, h, cache, writes=True, store=False):
+    def forward(self, ctx, x, h, cache, writes=True, store=False, defer=False):
         if not writes:
             raise AlofaError("unsupported", "this attention does not read another run's cache")
         n, dt = x.shape[0], self.rt.dtype
         group = ctx.groups[cache.group]
         sums = ctx.buf((n, self.rows), torch.float32)
-        self.qkv(sums, x, buf=ctx.buf)
+        # over prompt portions the kernel below adds the product's split sums up as it reads (1.388 -> 1.368 ms for a 2,048-token prompt of the
+        # 1k bench size); in steps of a few tokens the kernel that settles them first measured faster (0.373 against 0.381 ms a step at batch 8)
+        owed = self.qkv(sums, x, defer=n > DEFER_ABOVE, buf=ctx.buf)
         q = ctx.buf((n, self.q_dim), dt)
         rotated = self.rot_dims > 0
-        ops.qkv_prepare(q, cache.k, cache.v, sums, ctx.positions, group.slot_map, self.heads, self.kv_heads, self.dim, self.vdim, self.qk_norm, self.eps, self.coef, self.every,
-                        self.position.frequencies() if rotated else None, self.rot_dims, self.maps, self.q_weight, self.k_weight,
-                        float(getattr(self.position, "magnitude", 1.0)) if rotated else 1.0, self.values_from_keys, self.v_copies)
         g_off = self.q_dim + self.k_dim + self.v_dim  # the gates' column in the stacked projection's sums
+        gates, gates_at = (sums, g_off) if self.gate else (None, 0)
+        if owed is not None and self.gate:
+            gates, gates_at = ctx.buf((n, self.heads), torch.float32), 0  # the gates' logits, finished, for the kernel after the attention
+        ops.qkv_prepare(q, cache.k, cache.v, sums if owed is None else owed, ctx.positions, group.slot_map, self.heads, self.kv_heads, self.dim, self.vdim, self.qk_norm,
+                        self.eps, self.coef, self.every, self.position.frequencies() if rotated else None, self.rot_dims, self.maps, self.q_weight, self.k_weight,
+                        float(getattr(self.position, "magnitude", 1.0)) if rotated else 1.0, self.values_from_keys, self.v_copies,
+                        gates if owed is not None and self.gate else None, g_off)
         if self.tensor_cores or (self.dim == self.vdim and self.maps == 1 and not self.chunk):
             out = self.attend(ctx, q, cache, group)  # the tensor-core kernels in bfloat16 for the head sizes they are built for, else the every-size kernel
             if (self.gate or self.maps > 1) and not isinstance(out, torch.Tensor):
                 out = out.rows()
             if self.maps > 1:
                 a, out = out, ctx.buf((n, self.heads * self.vdim), dt)
-                ops.heads_finish(out, a, self.heads, self.kv_heads, self.vdim, self.maps, self.difference, self.eps, 1.0 - self.diff, sums if self.gate else None, g_off)
+                ops.heads_finish(out, a, self.heads, self.kv_heads, self.vdim, self.maps, self.difference, self.eps, 1.0 - self.diff, gates, gates_at)
             elif self.gate:
-                ops.head_gate(out, sums, g_off, self.heads, self.vdim)
+                ops.head_gate(out, gates, gates_at, self.heads, self.vdim)
         else:
             # the every-size kernel; what is still to be combined or gated stays fp32 until it has been
             plain = self.maps == 1 and not self.gate
@@ -183,11 +193,10 @@ class NormedAttention(PagedAttend, Part):
             if not plain:
                 out = ctx.buf((n, self.heads * self.vdim), dt)
                 ops.heads_finish(out, a, self.heads, self.kv_heads, self.vdim, self.maps, self.difference, self.eps, 1.0 - self.diff if self.maps == 2 else 1.0,
-                                 sums if self.gate else None, g_off)
+                                 gates, gates_at)
         if store:
-            self.out_store(h, out, buf=ctx.buf)
-        else:
-            add_into_stream(ctx, self.out_add, h, out)
+            return self.out_store(h, out, defer=defer, buf=ctx.buf)  # None, or the split sums a caller that asked for them adds up itself
+        add_into_stream(ctx, self.out_add, h, out)
 
 
 register_part("mixer", "normed_attention", NormedAttention)
