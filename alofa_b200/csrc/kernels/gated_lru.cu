@@ -86,6 +86,86 @@ __global__ void __launch_bounds__(LRU_OT) lru_gates_kernel(float* __restrict__ a
   }
 }
 
+// The same over prompt portions as a register-tiled product: a block of 256 threads takes 64 tokens and 128 outputs of one
+// block of the channels, a thread 4 tokens x 8 outputs of both gates (64 sums in registers); the inputs' and the weights'
+// tiles of 16 depth entries go through shared memory, so that 64 multiply-adds stand against five 16-byte loads.  Every
+// sum still takes its inputs in ascending order with the same multiply-adds as the kernel above: the same bits.
+constexpr int LRU_TILE_T = 64, LRU_TILE_O = 128, LRU_TILE_K = 16;
+
+__global__ void __launch_bounds__(256) lru_gates_tiled_kernel(float* __restrict__ a_out, float* __restrict__ b_out, const float* __restrict__ u, const float* __restrict__ wa,
+                                                              const float* __restrict__ wi, const float* __restrict__ ba, const float* __restrict__ bi,
+                                                              const float* __restrict__ lam, float decay_scale, int n_tokens, int W, int bs) {
+  __shared__ __align__(16) float us[LRU_TILE_K][LRU_TILE_T];   // inputs, [depth][token]
+  __shared__ __align__(16) float was[LRU_TILE_K][LRU_TILE_O];  // weights of the decay's gate, [depth][output]
+  __shared__ __align__(16) float wis[LRU_TILE_K][LRU_TILE_O];
+  pdl_begin();
+  const int t0 = blockIdx.x * LRU_TILE_T, blk = blockIdx.y, o0 = blockIdx.z * LRU_TILE_O;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // tx: outputs 4 tx .. 4 tx + 3 and the same 64 further on (no two lanes of a load on one bank), ty: 4 tokens
+  float sa[4][8], si[4][8];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) sa[r][c] = si[r][c] = 0.f;
+  const float* wab = wa + (size_t)blk * bs * bs;
+  const float* wib = wi + (size_t)blk * bs * bs;
+  for (int k0 = 0; k0 < bs; k0 += LRU_TILE_K) {
+    // inputs: 64 tokens x 16 depth entries, a thread four neighbouring depth entries of one token
+    {
+      const int r = threadIdx.x >> 2, kk = (threadIdx.x & 3) * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t0 + r < n_tokens && k0 + kk < bs) v = *reinterpret_cast<const float4*>(u + (size_t)(t0 + r) * W + blk * bs + k0 + kk);  // bs is a multiple of four
+      us[kk][r] = v.x, us[kk + 1][r] = v.y, us[kk + 2][r] = v.z, us[kk + 3][r] = v.w;
+    }
+    // weights: 16 depth entries x 128 outputs of both gates, 16 bytes a thread and round
+#pragma unroll
+    for (int e = threadIdx.x; e < LRU_TILE_K * LRU_TILE_O / 4; e += 256) {
+      const int kk = e / (LRU_TILE_O / 4), c = (e - kk * (LRU_TILE_O / 4)) * 4;
+      float4 va = make_float4(0.f, 0.f, 0.f, 0.f), vi = va;
+      if (k0 + kk < bs && o0 + c < bs) {
+        va = *reinterpret_cast<const float4*>(wab + (size_t)(k0 + kk) * bs + o0 + c);
+        vi = *reinterpret_cast<const float4*>(wib + (size_t)(k0 + kk) * bs + o0 + c);
+      }
+      *reinterpret_cast<float4*>(&was[kk][c]) = va;
+      *reinterpret_cast<float4*>(&wis[kk][c]) = vi;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < LRU_TILE_K; ++kk) {
+      const float4 x = *reinterpret_cast<const float4*>(&us[kk][ty * 4]);
+      const float4 a0 = *reinterpret_cast<const float4*>(&was[kk][tx * 4]), a1 = *reinterpret_cast<const float4*>(&was[kk][64 + tx * 4]);
+      const float4 i0 = *reinterpret_cast<const float4*>(&wis[kk][tx * 4]), i1 = *reinterpret_cast<const float4*>(&wis[kk][64 + tx * 4]);
+      const float xs[4] = {x.x, x.y, x.z, x.w};
+      const float as[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float is[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          sa[r][c] = fmaf(as[c], xs[r], sa[r][c]);
+          si[r][c] = fmaf(is[c], xs[r], si[r][c]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int o = o0 + (c < 4 ? tx * 4 + c : 64 + tx * 4 + c - 4);
+    if (o >= bs) continue;
+    const int ch = blk * bs + o;
+    const float bias_a = ba[ch], bias_i = bi[ch], rt = -decay_scale * lru_softplus(lam[ch]);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int t = t0 + ty * 4 + r;
+      if (t >= n_tokens) break;
+      const float gate_r = lru_sigmoid(sa[r][c] + bias_a), gate_i = lru_sigmoid(si[r][c] + bias_i);
+      const float log_a = rt * gate_r;
+      const size_t at = (size_t)t * W + ch;
+      a_out[at] = expf(log_a);
+      b_out[at] = sqrtf(-expm1f(2.0f * log_a)) * gate_i * u[at];
+    }
+  }
+}
+
 // The same for a handful of tokens (decode steps), where the kernel above would leave most of the device idle and every
 // thread waiting for its own weights: wa_rows, wi_rows [B][out][in] as the checkpoint has them; a warp takes an output
 // channel at a time, its lanes share the block's inputs four neighbours each (16-byte loads of the weights' rows), and
@@ -155,7 +235,13 @@ ALOFA_API int alofa_lru_gates(float* a_out, float* b_out, const float* u, const 
                wi_rows, ba, bi, lam, decay_scale, n_tokens, W, bs);
     return launch_status();
   }
-  // prompt portions: 32 tokens a block where their inputs fit in shared memory (with 8 every block pulled its 2 x bs x 128 weights
+  // prompt portions: the register-tiled kernel where blocks and rows lie on 16-byte boundaries
+  if (n_tokens >= 256 && bs % 4 == 0 && W % 4 == 0 && !(((uintptr_t)u | (uintptr_t)wa | (uintptr_t)wi) & 15)) {
+    launch_dep(lru_gates_tiled_kernel, dim3((n_tokens + LRU_TILE_T - 1) / LRU_TILE_T, blocks, (bs + LRU_TILE_O - 1) / LRU_TILE_O), 256, 0, stream, a_out, b_out, u, wa, wi,
+               ba, bi, lam, decay_scale, n_tokens, W, bs);
+    return launch_status();
+  }
+  // else 32 tokens a block where their inputs fit in shared memory (with 8 every block pulled its 2 x bs x 128 weights
   // from L2 for 8 tokens' worth of arithmetic, and L2 set the pace: 460 us for 4,096 tokens of 2,560 channels in blocks of 256)
   const size_t smem_long = (size_t)LRU_TT_LONG * bs * sizeof(float);
   if (n_tokens >= 8 * LRU_TT_LONG && smem_long <= 200 * 1024) {
