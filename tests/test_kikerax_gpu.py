@@ -435,6 +435,56 @@ def test_norm_on_a_sublayers_output_and_the_rows_the_next_one_reads(dtype, width
     assert torch.equal(z, x)
 
 
+class Owed:
+    """What a product leaves when its reader is to add its split sums up: planes [splits, rows, columns] and a bias."""
+
+    def __init__(self, sums, bias):
+        self.sums, self.splits, self.bias = sums, sums.shape[0], bias
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("width,splits", [(96, 2), (100, 3), (1024, 5), (2560, 9)])
+def test_the_output_norm_adds_owed_split_sums(dtype, width, splits):
+    from alofa_b200.csrc import ops
+
+    rng = np.random.default_rng(14)
+    n, eps = 11, 1e-5
+    h, wgt, bias = (rounded(rng.standard_normal(s) * 2, F32) for s in ((n, width), (width,), (width,)))
+    planes = rounded(rng.standard_normal((splits, n, width)), F32)
+    for b in (bias, None):
+        hd, x = dev(h, F32), torch.empty((n, width), dtype=dtype, device="cuda")
+        ops.sandwich_norm(hd, Owed(dev(planes, F32), dev(b, F32) if b is not None else None), dev(wgt, F32), eps, x)
+        y = planes.sum(axis=0) + (b if b is not None else 0.0)
+        assert_close(hd.cpu(), h + plain.rms_norm(y, wgt, eps), 2e-6, "stream")
+        assert_close(x.float().cpu(), rounded(hd.cpu().numpy(), dtype), 0, "the rows themselves")
+
+
+@pytest.mark.parametrize("maps,from_keys", [(2, False), (1, True), (1, False)])
+def test_queries_keys_and_values_from_owed_split_sums(maps, from_keys):
+    """The same q, keys, values and gate logits whether the stacked projection's sums come finished or as planes with a bias on top."""
+    from alofa_b200.csrc import ops
+
+    rng = np.random.default_rng(15)
+    H, G, d, dv, n, page = 4, 2, 24, 24 if from_keys else 40, 37, 16
+    ld = (H + G) * maps * d + (0 if from_keys else G * dv) + H
+    planes = rounded(rng.standard_normal((3, n, ld)), F32)
+    bias = rounded(rng.standard_normal(ld), F32)
+    whole = rounded(planes[0] + planes[1] + planes[2] + bias, F32)
+    wq, wk = dev(1 + 0.2 * rng.standard_normal(d), F32), dev(1 + 0.2 * rng.standard_normal(d), F32)
+    freq = dev(np.asarray(plain.rotary_frequencies(8, 100.0)[0], dtype=np.float32))
+    pos, slots = dev(np.arange(n, dtype=np.int32)), dev(rng.permutation(3 * page)[:n].astype(np.int32))
+    got = []
+    for sums in (dev(whole, F32), Owed(dev(planes, F32), dev(bias, F32))):
+        q = torch.zeros((n, H * maps * d), dtype=F32, device="cuda")
+        k, v = torch.zeros((3 * page, G * maps, d), dtype=F32, device="cuda"), torch.zeros((3 * page, G, dv), dtype=F32, device="cuda")
+        gates = torch.zeros((n, H), dtype=F32, device="cuda")
+        ops.qkv_prepare(q, k, v, sums, pos, slots, H, G, d, dv, True, 1e-5, 0.3, 5, freq, 8, maps, wq, wk, 1.1, from_keys, 1, gates, ld - H)
+        got.append([t.cpu().numpy() for t in (q, k, v, gates)])
+    for a, b, what in zip(got[0], got[1], ("q", "keys", "values", "gate logits")):
+        assert_close(b, a, 2e-6, what)
+    assert_close(got[1][3], whole[:, ld - H :], 1e-6, "gate logits")
+
+
 @pytest.mark.parametrize("cap", [0.5, 8.0, 30.0])
 def test_logit_cap(cap):
     from alofa_b200.csrc import ops
