@@ -622,7 +622,13 @@ class KernelClock:
     def _bytes(args, kwargs) -> int:
         import torch
 
-        return sum(a.numel() * a.element_size() for a in list(args) + list(kwargs.values()) if isinstance(a, torch.Tensor))
+        total = 0
+        for a in list(args) + list(kwargs.values()):
+            if isinstance(a, torch.Tensor):
+                total += a.numel() * a.element_size()
+            elif isinstance(getattr(a, "sums", None), torch.Tensor):  # a product's split sums, which the kernel adds up as it reads
+                total += a.sums.numel() * a.sums.element_size()
+        return total
 
     def ideal_us(self, name, args, kwargs, kv_rows: int) -> tuple:
         import torch
